@@ -13,7 +13,8 @@ Layers are grouped by what they need.  All runs of the schedule that need the
 same (kv heads, head size, window) share one group: one tensor
 [runs, pages, kv heads, 64, head size] for keys, one for values, one page list
 per sequence.  A group with a window gives pages back as they fall out of the
-window; a group of fixed-size state has one record per (run, sequence), zeroed
+window, a group whose queries see their own chunk of positions only gives back
+the pages of the chunks that are over; a group of fixed-size state has one record per (run, sequence), zeroed
 when a sequence opens.  A sequence is known by its slot, an index that is
 handed out by `open_sequence`, given back by `close_sequence` and then used
 again.
@@ -113,9 +114,12 @@ class KVGroup:
 
     def first_needed_page(self, next_pos: int) -> int:
         """Lowest page index that a query at `next_pos` or later can still read."""
-        if not self.need.window:
-            return 0
-        return max(0, next_pos - self.need.window + 1) // PAGE_SIZE
+        first = 0
+        if self.need.window:
+            first = max(0, next_pos - self.need.window + 1)
+        if self.need.chunk:
+            first = max(first, next_pos - next_pos % self.need.chunk)
+        return first // PAGE_SIZE
 
 
 class StateGroup:
@@ -291,7 +295,7 @@ class Cache:
         for slot, q in zip(slots, q_lens):
             self._length[slot] += q
         for g in self.kv_groups:
-            if not g.need.window:
+            if not (g.need.window or g.need.chunk):
                 continue
             for slot in slots:
                 keep_from = g.first_needed_page(int(self._length[slot]))
@@ -314,7 +318,7 @@ class Cache:
         return self._length[slots]
 
     def has_window_groups(self) -> bool:
-        return any(g.need.window for g in self.kv_groups)
+        return any(g.need.window or g.need.chunk for g in self.kv_groups)
 
     def reserve_one_each(self, slots: Sequence[int], lengths: np.ndarray) -> bool:
         """`reserve(slots, [1] * len(slots))` for the common decode step: a page is taken only by the

@@ -2,11 +2,16 @@
 //
 //   - keys of `kdim` and values of `vdim` numbers per head (the two may differ),
 //   - biases on the projected q, k and v,
+//   - an RMS norm of every q head and every k head over the head's numbers (one weight row for all q heads, one for all k
+//     heads), after the biases and before the rotation,
 //   - a rotation of the first `rot` dimensions of q and k in either pair layout, cosines and sines
 //     multiplied by a constant `magnitude`,
 //   - a score scale given by the caller,
 //   - a mixing of the heads' scaled scores before the softmax, s_h <- sum_g mix[h][g] s_g,
 //   - a window (query at position p sees keys j with 0 <= p - j < window),
+//   - chunks (query at position p sees keys j <= p of its own chunk only, floor(j / chunk) = floor(p / chunk), positions
+//     counted from the start of the sequence),
+//   - a cap on the scores, s <- cap tanh(s / cap), after the scale (and the mixing),
 //   - a sink per head: exp(sink_h) joins the softmax's denominator and nothing else,
 //   - a gate on the result, out *= sigmoid(gate), and a constant factor `out_scale`.
 //
@@ -29,9 +34,10 @@ template <typename T>
 __global__ void qkv_prep_kernel(T* __restrict__ qkv, int row_stride, const float* __restrict__ bias,
                                 const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                 const int* __restrict__ block_table, int table_width, T* __restrict__ k_pages,
-                                T* __restrict__ v_pages, const float* __restrict__ inv_freq, float magnitude, int H, int K,
+                                T* __restrict__ v_pages, const float* __restrict__ inv_freq, float magnitude,
+                                const float* __restrict__ q_norm, const float* __restrict__ k_norm, float norm_eps, int H, int K,
                                 int kdim, int vdim, int rot, int interleaved, int page_size) {
-  extern __shared__ float trig[];  // cos[rot/2], sin[rot/2], both times the magnitude
+  extern __shared__ float trig[];  // cos[rot/2], sin[rot/2], both times the magnitude; then 1 / rms of every q and k head
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   const int half = rot >> 1;
@@ -44,8 +50,23 @@ __global__ void qkv_prep_kernel(T* __restrict__ qkv, int row_stride, const float
     cs[j] = c * magnitude;
     sn[j] = s * magnitude;
   }
-  __syncthreads();
   T* row = qkv + (size_t)t * row_stride;
+  float* inv_rms = trig + rot;
+  if (q_norm != nullptr || k_norm != nullptr) {  // a warp per head, the sums in lane order and then by the warp's tree
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int h = warp; h < H + K; h += nwarps) {
+      const T* head = row + (size_t)h * kdim;
+      const float* b = bias ? bias + (size_t)h * kdim : nullptr;
+      float ss = 0.f;
+      for (int i = lane; i < kdim; i += 32) {
+        const float x = to_f32(head[i]) + (b ? b[i] : 0.f);
+        ss += x * x;
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) inv_rms[h] = ((h < H ? q_norm : k_norm) != nullptr) ? 1.0f / sqrtf(ss / (float)kdim + norm_eps) : 1.f;
+    }
+  }
+  __syncthreads();
   const int page = block_table[(size_t)tok_seq[t] * table_width + pos / page_size];
   const int in_page = pos % page_size;
   // q and k heads: one thread per rotated pair or per unrotated value
@@ -54,17 +75,25 @@ __global__ void qkv_prep_kernel(T* __restrict__ qkv, int row_stride, const float
     const int h = idx / per_head, e = idx - h * per_head;
     T* head = row + (size_t)h * kdim;
     const float* b = bias ? bias + (size_t)h * kdim : nullptr;
+    const float* nw = h < H ? q_norm : k_norm;
+    const float inv = nw ? inv_rms[h] : 1.f;
     T* dst = h < H ? head : k_pages + (((size_t)page * K + (h - H)) * page_size + in_page) * kdim;
     if (e < half) {
       const int i0 = interleaved ? 2 * e : e;
       const int i1 = interleaved ? 2 * e + 1 : e + half;
-      const float x0 = to_f32(head[i0]) + (b ? b[i0] : 0.f);
-      const float x1 = to_f32(head[i1]) + (b ? b[i1] : 0.f);
+      float x0 = to_f32(head[i0]) + (b ? b[i0] : 0.f);
+      float x1 = to_f32(head[i1]) + (b ? b[i1] : 0.f);
+      if (nw) {
+        x0 = x0 * inv * nw[i0];
+        x1 = x1 * inv * nw[i1];
+      }
       dst[i0] = from_f32<T>(x0 * cs[e] - x1 * sn[e]);
       dst[i1] = from_f32<T>(x1 * cs[e] + x0 * sn[e]);
     } else {
       const int i = rot + (e - half);
-      dst[i] = from_f32<T>(to_f32(head[i]) + (b ? b[i] : 0.f));
+      float x = to_f32(head[i]) + (b ? b[i] : 0.f);
+      if (nw) x = x * inv * nw[i];
+      dst[i] = from_f32<T>(x);
     }
   }
   const T* vrow = row + (size_t)(H + K) * kdim;
@@ -77,25 +106,25 @@ __global__ void qkv_prep_kernel(T* __restrict__ qkv, int row_stride, const float
 
 RL_API int rl_qkv_prep(void* qkv, int dtype, int row_stride, const float* bias, const int* tok_pos, const int* tok_seq,
                        const int* block_table, int table_width, void* k_pages, void* v_pages, const float* inv_freq,
-                       float magnitude, int n_tokens, int H, int K, int kdim, int vdim, int rot, int interleaved, int page_size,
-                       cudaStream_t stream) {
+                       float magnitude, const float* q_norm, const float* k_norm, float norm_eps, int n_tokens, int H, int K, int kdim,
+                       int vdim, int rot, int interleaved, int page_size, cudaStream_t stream) {
   if (n_tokens <= 0 || H <= 0 || K <= 0 || kdim <= 0 || vdim <= 0 || page_size <= 0 || table_width <= 0)
     RL_REFUSE(1, "qkv_prep: T=%d H=%d K=%d kdim=%d vdim=%d page=%d", n_tokens, H, K, kdim, vdim, page_size);
   if (rot < 0 || rot > kdim || (rot & 1)) RL_REFUSE(2, "qkv_prep: %d rotated dimensions do not fit a head of %d", rot, kdim);
   if (row_stride < (H + K) * kdim + K * vdim) RL_REFUSE(3, "qkv_prep: row stride %d too small", row_stride);
   if (rot > 0 && inv_freq == nullptr) RL_REFUSE(4, "qkv_prep: no frequency table");
   if (!block_table || !k_pages || !v_pages || !tok_pos || !tok_seq) RL_REFUSE(5, "qkv_prep: pages, page table and positions are needed");
-  const size_t smem = (size_t)rot * sizeof(float);
-  if (smem > 48 * 1024) RL_REFUSE(6, "qkv_prep: rotary size %d too large", rot);
+  const size_t smem = ((size_t)rot + H + K) * sizeof(float);
+  if (smem > 48 * 1024) RL_REFUSE(6, "qkv_prep: rotary size %d or %d heads too large", rot, H + K);
   const int threads = 256;
   if (dtype == RL_BF16)
     qkv_prep_kernel<bf16><<<n_tokens, threads, smem, stream>>>((bf16*)qkv, row_stride, bias, tok_pos, tok_seq, block_table, table_width,
-                                                               (bf16*)k_pages, (bf16*)v_pages, inv_freq, magnitude, H, K, kdim, vdim, rot,
-                                                               interleaved, page_size);
+                                                               (bf16*)k_pages, (bf16*)v_pages, inv_freq, magnitude, q_norm, k_norm, norm_eps, H, K,
+                                                               kdim, vdim, rot, interleaved, page_size);
   else if (dtype == RL_F32)
     qkv_prep_kernel<float><<<n_tokens, threads, smem, stream>>>((float*)qkv, row_stride, bias, tok_pos, tok_seq, block_table, table_width,
-                                                                (float*)k_pages, (float*)v_pages, inv_freq, magnitude, H, K, kdim, vdim, rot,
-                                                                interleaved, page_size);
+                                                                (float*)k_pages, (float*)v_pages, inv_freq, magnitude, q_norm, k_norm, norm_eps, H, K,
+                                                                kdim, vdim, rot, interleaved, page_size);
   else
     RL_REFUSE(7, "qkv_prep: unknown dtype %d", dtype);
   RL_LAUNCH_RESULT();
@@ -110,7 +139,7 @@ __global__ void attn_ext_kernel(const T* __restrict__ q, int q_stride, const T* 
                                 const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_seq,
                                 const int* __restrict__ tok_pos, const float* __restrict__ sink, const float* __restrict__ mix,
                                 const T* __restrict__ gate, int gate_stride, float out_scale, T* __restrict__ out, int out_stride,
-                                int H, int K, int kdim, int vdim, int page_size, int window, float scale) {
+                                int H, int K, int kdim, int vdim, int page_size, int window, float scale, int chunk, float softcap) {
   extern __shared__ float smem[];  // q of the block's heads [HB][kdim], then (with mix) scores [HB][32]
   const int lane = threadIdx.x;
   const int hb = threadIdx.y, HB = blockDim.y;
@@ -124,7 +153,8 @@ __global__ void attn_ext_kernel(const T* __restrict__ q, int q_stride, const T* 
   for (int i = lane; i < kdim; i += 32) q_s[i] = to_f32(qh[i]);
   __syncwarp();
 
-  const int first = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
+  int first = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
+  if (chunk != 0) first = max(first, pos - pos % chunk);
   float m = -INFINITY, l = 0.f;
   if (sink != nullptr) {  // the sink is a key without a value whose score is sink[h]
     m = sink[h];
@@ -153,6 +183,7 @@ __global__ void attn_ext_kernel(const T* __restrict__ q, int q_stride, const T* 
       for (int g = 0; g < HB; ++g) mixed += mix[h * HB + g] * sc[g * 32 + lane];
       s = mixed;
     }
+    if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     if (!valid) s = -INFINITY;
     const float m_new = fmaxf(m, warp_max(s));  // finite: the group holds at least key `base`
     const float alpha = expf(m - m_new);        // 0 for the first group without a sink, where m is -inf
@@ -191,13 +222,13 @@ __global__ void attn_ext_kernel(const T* __restrict__ q, int q_stride, const T* 
 RL_API int rl_attn_ext(const void* q, int dtype, int q_stride, const void* k_pages, const void* v_pages, const int* block_table,
                        int table_width, const int* tok_seq, const int* tok_pos, const float* sink, const float* mix,
                        const void* gate, int gate_stride, float out_scale, void* out, int out_stride, int n_tokens, int H, int K,
-                       int kdim, int vdim, int page_size, int window, float scale, cudaStream_t stream) {
+                       int kdim, int vdim, int page_size, int window, float scale, int chunk, float softcap, cudaStream_t stream) {
   if (n_tokens <= 0 || H <= 0 || K <= 0 || kdim <= 0 || vdim <= 0 || page_size <= 0)
     RL_REFUSE(1, "attn_ext: T=%d H=%d K=%d kdim=%d vdim=%d page=%d", n_tokens, H, K, kdim, vdim, page_size);
   if (H % K) RL_REFUSE(2, "attn_ext: %d query heads are not a multiple of %d kv heads", H, K);
   if (vdim > 32 * EXT_MAX_V_PER_LANE) RL_REFUSE(3, "attn_ext: value size %d exceeds %d", vdim, 32 * EXT_MAX_V_PER_LANE);
   if (H > 65535) RL_REFUSE(4, "attn_ext: %d heads exceed 65535", H);
-  if (window < 0) RL_REFUSE(5, "attn_ext: negative window");
+  if (window < 0 || chunk < 0) RL_REFUSE(5, "attn_ext: negative window or chunk");
   if (mix != nullptr && H > 32) RL_REFUSE(6, "attn_ext: scores of %d heads cannot be mixed (at most 32)", H);
   const int HB = mix != nullptr ? H : 1;
   dim3 grid(n_tokens, H / HB), block(32, HB);
@@ -207,12 +238,12 @@ RL_API int rl_attn_ext(const void* q, int dtype, int q_stride, const void* k_pag
     attn_ext_kernel<bf16><<<grid, block, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages,
                                                          block_table, table_width, tok_seq, tok_pos, sink, mix, (const bf16*)gate,
                                                          gate_stride, out_scale, (bf16*)out, out_stride, H, K, kdim, vdim, page_size,
-                                                         window, scale);
+                                                         window, scale, chunk, softcap);
   else if (dtype == RL_F32)
     attn_ext_kernel<float><<<grid, block, smem, stream>>>((const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages,
                                                           block_table, table_width, tok_seq, tok_pos, sink, mix, (const float*)gate,
                                                           gate_stride, out_scale, (float*)out, out_stride, H, K, kdim, vdim, page_size,
-                                                          window, scale);
+                                                          window, scale, chunk, softcap);
   else
     RL_REFUSE(8, "attn_ext: unknown dtype %d", dtype);
   RL_LAUNCH_RESULT();

@@ -2,7 +2,7 @@
 //
 //   moe_gemm_mma     the products of a routed feed-forward: a block takes one row tile of the plan that `moe_plan`
 //                    left on the device (rows of ONE expert, gathered through `order`) and 64 columns of that expert's
-//                    matrix; with ACT it computes the gate and the up product together and writes silu(gate) * up
+//                    matrix; with ACT it computes the gate and the up product together and writes gated_act(gate, up) (silu(gate) * up, or the clamped form)
 //   head_linear_mma  out[t, h, :] = W[h] x[t, h, :] for every head h, optionally times sigmoid(gate[t, h, :])
 //
 // Both are the same tile loop: BM rows x BN columns per block, k in slices of 64 through two stages of shared memory
@@ -130,7 +130,7 @@ struct Tile {
 template <int BM, int BN, int WM, int WN, bool ACT, typename TO>
 __global__ void __launch_bounds__(WM * WN * 32)
 moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const int* __restrict__ order, int gather_div, const bf16* __restrict__ w,
-                    const bf16* __restrict__ w2, TO* __restrict__ out, int ldo, const int* __restrict__ tiles, int N, int K) {
+                    const bf16* __restrict__ w2, TO* __restrict__ out, int ldo, const int* __restrict__ tiles, int N, int K, float act_alpha, float act_limit) {
   using T = Tile<BM, BN, WM, WN, ACT>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ const bf16* a_rows[BM];
@@ -158,14 +158,15 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const int* __restrict__
           const int n = n0 + wn * T::NT * 8 + j * 8 + 2 * t4 + c;
           if (n >= N) continue;
           float v = acc[i][j][2 * hh + c];
-          if (ACT) v = v * (1.0f / (1.0f + expf(-v))) * acc2[ACT ? i : 0][ACT ? j : 0][2 * hh + c];
+          if (ACT) v = gated_act(v, acc2[ACT ? i : 0][ACT ? j : 0][2 * hh + c], act_alpha, act_limit);
           out[(size_t)(r0 + r) * ldo + n] = from_f32<TO>(v);
         }
     }
 }
 
 RL_API int rl_moe_gemm_mma(const void* x, int ldx, const int* order, int gather_div, const void* w, const void* w2, void* out,
-                           int out_dtype, int ldo, const int* tiles, int max_tiles, int tile_rows, int N, int K, cudaStream_t stream) {
+                           int out_dtype, int ldo, const int* tiles, int max_tiles, int tile_rows, int N, int K, float act_alpha, float act_limit,
+                           cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0 || K <= 0 || gather_div <= 0) RL_REFUSE(1, "moe_gemm_mma: tiles=%d N=%d K=%d div=%d", max_tiles, N, K, gather_div);
   if (max_tiles > 65535) RL_REFUSE(2, "moe_gemm_mma: %d row tiles exceed the grid", max_tiles);
   if (K % 8 || ldx % 8) RL_REFUSE(3, "moe_gemm_mma: k = %d or a row stride of %d elements breaks 16-byte alignment", K, ldx);
@@ -178,7 +179,7 @@ RL_API int rl_moe_gemm_mma(const void* x, int ldx, const int* order, int gather_
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)      \
       RL_REFUSE(5, "moe_gemm_mma: cannot get %zu bytes of shared memory", smem);                                                    \
     RL_LAUNCH_CHECK(rl_launch<false>(kern, grid, WM * WN * 32, smem, stream, (const bf16*)x, ldx, order, gather_div, (const bf16*)w, \
-                                     (const bf16*)w2, (TO*)out, ldo, tiles, N, K));                                                 \
+                                     (const bf16*)w2, (TO*)out, ldo, tiles, N, K, act_alpha, act_limit));                           \
     return 0;                                                                                                                       \
   } while (0)
   const bool act = w2 != nullptr;

@@ -233,6 +233,27 @@ moe_plan_kernel(const int* __restrict__ ids, int n, int E, int* __restrict__ ord
   }
 }
 
+// ---------------------------------------------------------------- experts chosen by a table instead of a router
+// ids[t][j] = table[token[t]][j], every chosen expert with the weight 1 / top.
+__global__ void moe_table_lookup_kernel(const int* __restrict__ tokens, const int* __restrict__ table, int top, int n, int E,
+                                        int* __restrict__ ids, float* __restrict__ weights) {
+  pdl_trigger();
+  pdl_wait();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n * top) return;
+  const int t = idx / top, j = idx - t * top;
+  const int e = table[(size_t)tokens[t] * top + j];
+  ids[idx] = min(max(e, 0), E - 1);  // (the loader has checked the table; a stray id must still not index outside the weights)
+  weights[idx] = 1.0f / (float)top;
+}
+
+RL_API int rl_moe_table_lookup(const int* tokens, const int* table, int top, int n_tokens, int E, int* ids, float* weights, cudaStream_t stream) {
+  if (n_tokens <= 0 || top <= 0 || E <= 0) RL_REFUSE(1, "moe_table_lookup: T=%d top=%d E=%d", n_tokens, top, E);
+  const int total = n_tokens * top;
+  RL_LAUNCH_CHECK(rl_launch(moe_table_lookup_kernel, (total + 255) / 256, 256, 0, stream, tokens, table, top, n_tokens, E, ids, weights));
+  return 0;
+}
+
 RL_API int rl_moe_tile_rows() { return MOE_TM; }
 
 RL_API int rl_moe_plan(const int* ids, int n, int E, int* order, int* place, int* tiles, int tile_rows, cudaStream_t stream) {
@@ -245,12 +266,14 @@ RL_API int rl_moe_plan(const int* ids, int n, int E, int* order, int* place, int
 
 // ---------------------------------------------------------------- all experts' products in one launch
 // Row r of the layout belongs to pair order[r]; its input row is x[order[r] / gather_div] when `order` is given
-// (the token's activations), else x[r].  w: [E, N, K]; with ACT also w2: [E, N, K] and out = silu(x w^T) * (x w2^T).
+// (the token's activations), else x[r].  w: [E, N, K]; with ACT also w2: [E, N, K] and out = gated_act(x w^T, x w2^T): silu(g) * u,
+// or with a limit the clamped form (common.cuh).
 // blockIdx.y walks the tiles of the plan; a block beyond the plan's count leaves.
 template <typename TA, typename TO, bool ACT>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TA* __restrict__ x, int ldx, const int* __restrict__ order, int gather_div, const TA* __restrict__ w,
-                const TA* __restrict__ w2, TO* __restrict__ out, int ldo, const int* __restrict__ tiles, int N, int K) {
+                const TA* __restrict__ w2, TO* __restrict__ out, int ldo, const int* __restrict__ tiles, int N, int K, float act_alpha,
+                float act_limit) {
   __shared__ float xs[MOE_TK][MOE_TM + 4];
   __shared__ float ws[MOE_TK][MOE_TN + 4];
   __shared__ float ws2[ACT ? MOE_TK : 1][MOE_TN + 4];
@@ -317,7 +340,7 @@ moe_gemm_kernel(const TA* __restrict__ x, int ldx, const int* __restrict__ order
       const int n = n0 + tx * 4 + j;
       if (n >= N) continue;
       float v = acc[i][j];
-      if (ACT) v = v * (1.0f / (1.0f + expf(-v))) * acc2[i][j];
+      if (ACT) v = gated_act(v, acc2[i][j], act_alpha, act_limit);
       out[(size_t)(r0 + r) * ldo + n] = from_f32<TO>(v);
     }
   }
@@ -325,13 +348,14 @@ moe_gemm_kernel(const TA* __restrict__ x, int ldx, const int* __restrict__ order
 
 // (the plan's tiles must be MOE_TM rows high: `rl_moe_tile_rows`)
 RL_API int rl_moe_gemm(const void* x, int ldx, int dtype, const int* order, int gather_div, const void* w, const void* w2,
-                       void* out, int out_dtype, int ldo, const int* tiles, int max_tiles, int N, int K, cudaStream_t stream) {
+                       void* out, int out_dtype, int ldo, const int* tiles, int max_tiles, int N, int K, float act_alpha, float act_limit,
+                       cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0 || K <= 0 || gather_div <= 0) RL_REFUSE(1, "moe_gemm: tiles=%d N=%d K=%d div=%d", max_tiles, N, K, gather_div);
   if (max_tiles > 65535) RL_REFUSE(2, "moe_gemm: %d row tiles exceed the grid", max_tiles);
   dim3 grid((N + MOE_TN - 1) / MOE_TN, max_tiles);
 #define RL_MG(TA, TO, ACT)                                                                                                  \
   RL_LAUNCH_CHECK(rl_launch<false>(moe_gemm_kernel<TA, TO, ACT>, grid, 256, 0, stream, (const TA*)x, ldx, order, gather_div, \
-                                   (const TA*)w, (const TA*)w2, (TO*)out, ldo, tiles, N, K))
+                                   (const TA*)w, (const TA*)w2, (TO*)out, ldo, tiles, N, K, act_alpha, act_limit))
   if (dtype == RL_BF16 && out_dtype == RL_BF16 && w2) RL_MG(bf16, bf16, true);
   else if (dtype == RL_BF16 && out_dtype == RL_BF16) RL_MG(bf16, bf16, false);
   else if (dtype == RL_BF16 && out_dtype == RL_F32 && !w2) RL_MG(bf16, float, false);

@@ -1101,6 +1101,20 @@ def moe_router(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], n
     return ids, weights, gate
 
 
+def moe_table_lookup(tokens: torch.Tensor, table: torch.Tensor, n_experts: int):
+    """tokens int32 [T], table int32 [vocab, top] -> (ids int32 [T, top] = table[tokens], weights float32 [T, top] = 1 / top)."""
+    _cuda(tokens, "moe_table_lookup tokens", torch.int32)
+    _cuda(table, "moe_table_lookup table", torch.int32)
+    _need(tokens.dim() == 1 and table.dim() == 2, "moe_table_lookup: tokens[T] and table[vocab, top] expected")
+    T, top = tokens.numel(), table.shape[1]
+    ids = torch.empty((T, top), dtype=torch.int32, device=tokens.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=tokens.device)
+    lib = build.load("moe")
+    rc = lib.rl_moe_table_lookup(_p(tokens), _p(table), c_int(top), c_int(T), c_int(n_experts), _p(ids), _p(weights), _stream())
+    _check(lib, rc, "moe_table_lookup")
+    return ids, weights
+
+
 MOE_MMA_TILE_ROWS = (32, 128)  # tile heights the tensor-core products are built for
 
 
@@ -1128,11 +1142,12 @@ def moe_plan(ids: torch.Tensor, n_experts: int, tile_rows: int = 0):
 
 def moe_gemm(
     x: torch.Tensor, w: torch.Tensor, tiles: torch.Tensor, max_tiles: int, n_rows: int, order: Optional[torch.Tensor] = None,
-    gather_div: int = 1, w2: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, tile_rows: int = 0,
+    gather_div: int = 1, w2: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, tile_rows: int = 0, act=None,
 ) -> torch.Tensor:
     """out[r] = w[expert of r] . x[row of r] for the n_rows rows of a plan's layout; w: [E, N, K].
 
-    order given: row r reads x[order[r] // gather_div], else x[r].  w2 given: out = silu(w x) * (w2 x).
+    order given: row r reads x[order[r] // gather_div], else x[r].  w2 given: out = silu(w x) * (w2 x), or with act = (alpha, limit)
+    g s(alpha g) (u + 1), g = min(w x, limit), u = clamp(w2 x, -limit, limit).
     tile_rows: the height of the plan's tiles; bfloat16 operands whose rows can be moved in 16-byte pieces go to the
     tensor cores if it is one of MOE_MMA_TILE_ROWS, everything else to the plain kernel (which wants its own height)."""
     _cuda(x, "moe_gemm x", contiguous=False)
@@ -1145,11 +1160,12 @@ def moe_gemm(
     out_dtype = out_dtype or x.dtype
     out = torch.empty((n_rows, N), dtype=out_dtype, device=x.device)
     tile_rows = tile_rows or moe_tile_rows()
+    alpha, limit = _act(act)
     if x.dtype == torch.bfloat16 and tile_rows in MOE_MMA_TILE_ROWS and grouped_gemm_takes(K, x.stride(0), 0) and x.data_ptr() % 16 == 0:
         lib = build.load("grouped_gemm")
         rc = lib.rl_moe_gemm_mma(
             _p(x), c_int(x.stride(0)), _p(order), c_int(gather_div), _p(w), _p(w2), _p(out), c_int(_dt(out, "moe_gemm out")), c_int(N),
-            _p(tiles), c_int(max_tiles), c_int(tile_rows), c_int(N), c_int(K), _stream(),
+            _p(tiles), c_int(max_tiles), c_int(tile_rows), c_int(N), c_int(K), alpha, limit, _stream(),
         )
         _check(lib, rc, "moe_gemm_mma")
         return out
@@ -1157,7 +1173,7 @@ def moe_gemm(
     lib = build.load("moe")
     rc = lib.rl_moe_gemm(
         _p(x), c_int(_rows(x, "moe_gemm x")), c_int(_dt(x, "moe_gemm")), _p(order), c_int(gather_div), _p(w), _p(w2), _p(out),
-        c_int(_dt(out, "moe_gemm out")), c_int(N), _p(tiles), c_int(max_tiles), c_int(N), c_int(K), _stream(),
+        c_int(_dt(out, "moe_gemm out")), c_int(N), _p(tiles), c_int(max_tiles), c_int(N), c_int(K), alpha, limit, _stream(),
     )
     _check(lib, rc, "moe_gemm")
     return out
@@ -1254,9 +1270,11 @@ def _check_kv_pages(k_pages, v_pages, dtype, K, kdim, vdim, what):
 def qkv_prep(
     qkv: torch.Tensor, bias: Optional[torch.Tensor], tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
     k_pages: torch.Tensor, v_pages: torch.Tensor, inv_freq: Optional[torch.Tensor], magnitude: float, num_heads: int, num_kv_heads: int,
-    kdim: int, vdim: int, rotary_dim: int, interleaved: bool,
+    kdim: int, vdim: int, rotary_dim: int, interleaved: bool, q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None,
+    norm_eps: float = 0.0,
 ) -> None:
-    """qkv[T, >= (H + K) kdim + K vdim]: add `bias` (float32, one number per column, or None), rotate the first `rotary_dim`
+    """qkv[T, >= (H + K) kdim + K vdim]: add `bias` (float32, one number per column, or None), divide every q head (k head) by its
+    root mean square and multiply it by `q_norm` (`k_norm`; float32 [kdim], None: no norm), rotate the first `rotary_dim`
     dimensions of every q head (in place) and k head by position * inv_freq, cosines and sines times `magnitude`, and store
     k and v at each token's place in the paged cache (k_pages [pages, K, PAGE_SIZE, kdim], v_pages [..., vdim])."""
     _cuda(qkv, "qkv_prep qkv", contiguous=False)
@@ -1276,11 +1294,15 @@ def qkv_prep(
     if rotary_dim:
         _cuda(inv_freq, "qkv_prep inv_freq", torch.float32)
         _need(inv_freq.numel() == rotary_dim // 2, "qkv_prep: inv_freq must hold rotary_dim/2 values")
+    for name, w in (("q_norm", q_norm), ("k_norm", k_norm)):
+        if w is not None:
+            _cuda(w, f"qkv_prep {name}", torch.float32)
+            _need(w.numel() == kdim, f"qkv_prep: {name} must hold one weight per number of a head ({kdim})")
     lib = build.load("attention_ext")
     rc = lib.rl_qkv_prep(
         _p(qkv), c_int(_dt(qkv, "qkv_prep")), c_int(stride), _p(bias), _p(tok_pos), _p(tok_seq), _p(block_table), c_int(block_table.shape[1]),
-        _p(k_pages), _p(v_pages), _p(inv_freq if rotary_dim else None), c_float(magnitude), c_int(T), c_int(num_heads), c_int(num_kv_heads),
-        c_int(kdim), c_int(vdim), c_int(rotary_dim), c_int(1 if interleaved else 0), c_int(PAGE_SIZE), _stream(),
+        _p(k_pages), _p(v_pages), _p(inv_freq if rotary_dim else None), c_float(magnitude), _p(q_norm), _p(k_norm), c_float(norm_eps), c_int(T), c_int(num_heads),
+        c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(rotary_dim), c_int(1 if interleaved else 0), c_int(PAGE_SIZE), _stream(),
     )
     _check(lib, rc, "qkv_prep")
 
@@ -1288,9 +1310,12 @@ def qkv_prep(
 def attn_ext(
     q: torch.Tensor, k_pages, v_pages, block_table, tok_seq, tok_pos, num_heads: int, num_kv_heads: int, kdim: int, vdim: int,
     scale: float, window: int = 0, sink: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
-    gate: Optional[torch.Tensor] = None, out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
+    gate: Optional[torch.Tensor] = None, out_scale: float = 1.0, out: Optional[torch.Tensor] = None, chunk: int = 0, softcap: float = 0.0,
 ) -> torch.Tensor:
     """Attention of each token over its sequence's cached keys, both element types, prompts and decoding.
+
+    window: 0, or how many of the last positions a query sees.  chunk: 0, or the size of the chunks (counted from position 0)
+    outside of which a query sees nothing.  softcap: 0, or the cap c of s <- c tanh(s / c) on the scaled scores.
 
     q: [T, >= H kdim] rows.  sink: float32 [H] or None.  mix: float32 [H, H] or None (scores of the heads are mixed before the
     softmax).  gate: [T, >= H vdim] rows of q's type or None: the result is multiplied by sigmoid(gate).  out: [T, H vdim] rows
@@ -1323,7 +1348,7 @@ def attn_ext(
     rc = lib.rl_attn_ext(
         _p(q), c_int(_dt(q, "attn_ext")), c_int(qs), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]), _p(tok_seq),
         _p(tok_pos), _p(sink), _p(mix), _p(gate), c_int(gs), c_float(out_scale), _p(out), c_int(out.stride(0)), c_int(T), c_int(num_heads),
-        c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _stream(),
+        c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(PAGE_SIZE), c_int(window), c_float(scale), c_int(chunk), c_float(softcap), _stream(),
     )
     _check(lib, rc, "attn_ext")
     return out
@@ -1452,6 +1477,140 @@ def min_gru(
     )
     _check(lib, rc, "min_gru")
     return out
+
+
+# ------------------------------------------------------------------ recurrences with gates per token (csrc/gated_recurrent.cu)
+def gla_log_decay(z: torch.Tensor, bias: Optional[torch.Tensor], tau: float) -> torch.Tensor:
+    """log a = logsigmoid(z + bias) / tau as float32 [T, n]; z: [T, n] rows of the run's type (a strided view is taken as it is)."""
+    _cuda(z, "gla_log_decay z", contiguous=False)
+    zs = _rows(z, "gla_log_decay z")
+    T, n = z.shape
+    if bias is not None:
+        _cuda(bias, "gla_log_decay bias", torch.float32)
+        _need(bias.numel() == n, "gla_log_decay: one bias per column")
+    out = torch.empty((T, n), dtype=torch.float32, device=z.device)
+    lib = build.load("gated_recurrent")
+    rc = lib.rl_gla_log_decay(_p(z), c_int(_dt(z, "gla_log_decay")), c_int(zs), _p(bias), c_float(tau), _p(out), c_int(T), c_int(n), _stream())
+    _check(lib, rc, "gla_log_decay")
+    return out
+
+
+def mlstm_gates(
+    gi: torch.Tensor, gf: torch.Tensor, bias_i: Optional[torch.Tensor], bias_f: Optional[torch.Tensor], cap: float, m_state: torch.Tensor,
+    slot_ids: torch.Tensor, seq_start: torch.Tensor,
+):
+    """The gates of a matrix memory.  gi, gf: [T, H] views of one projection's rows (the raw input and forget gates); biases float32 [H].
+    With i = cap tanh((gi + b_i) / cap), f = logsigmoid(cap tanh((gf + b_f) / cap)) and the running maximum m_t = max(f_t + m_(t-1), i_t)
+    carried in m_state float32 [slots, H]: returns (log_a = f + m_(t-1) - m_t, b = exp(i - m_t), m), each float32 [T, H]."""
+    _cuda(gi, "mlstm_gates gi", contiguous=False)
+    _cuda(gf, "mlstm_gates gf", gi.dtype, contiguous=False)
+    stride = _rows(gi, "mlstm_gates gi")
+    _need(_rows(gf, "mlstm_gates gf") == stride and gf.shape == gi.shape, "mlstm_gates: the two gates must be views of the same rows")
+    T, H = gi.shape
+    for name, b in (("bias_i", bias_i), ("bias_f", bias_f)):
+        if b is not None:
+            _cuda(b, f"mlstm_gates {name}", torch.float32)
+            _need(b.numel() == H, "mlstm_gates: one bias per head")
+    _cuda(m_state, "mlstm_gates m_state", torch.float32)
+    _need(m_state.dim() == 2 and m_state.shape[1] == H, f"mlstm_gates: m_state {tuple(m_state.shape)} is not [slots, {H}]")
+    _cuda(slot_ids, "mlstm_gates slot_ids", torch.int32)
+    _cuda(seq_start, "mlstm_gates seq_start", torch.int32)
+    S = slot_ids.numel()
+    _need(seq_start.numel() == S + 1, "mlstm_gates: seq_start must hold one more entry than there are sequences")
+    log_a, b, m = (torch.empty((T, H), dtype=torch.float32, device=gi.device) for _ in range(3))
+    lib = build.load("gated_recurrent")
+    rc = lib.rl_mlstm_gates(
+        _p(gi), _p(gf), c_int(_dt(gi, "mlstm_gates")), c_int(stride), _p(bias_i), _p(bias_f), c_float(cap), _p(m_state), _p(slot_ids),
+        _p(seq_start), _p(log_a), _p(b), _p(m), c_int(S), c_int(H), _stream(),
+    )
+    _check(lib, rc, "mlstm_gates")
+    return log_a, b, m
+
+
+def gated_attn(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay: torch.Tensor, in_scale: Optional[torch.Tensor], state: torch.Tensor,
+    slot_ids: torch.Tensor, seq_start: torch.Tensor, num_heads: int, dim: int, vdim: int, q_scale: float = 1.0, ext: bool = False,
+) -> torch.Tensor:
+    """S_t = diag(a_t) S_(t-1) + b_t k_t v_t^T, o_t = S_t^T (q_scale q_t) through the sequences' states, token by token.
+
+    q, k: [T, H dim], v: [T, H vdim], views of one projection's rows.  log_decay: float32 [T, H dim] (a per key channel) or [T, H]
+    (a per head), a = exp(log_decay).  in_scale: float32 [T, H] (b) or None (1).  ext: the state has one more column, fed with
+    v = 1, and so has the result.  state: float32 [slots, H, dim, vdim (+1)].  Returns float32 [T, H (vdim (+1))]."""
+    for name, t, n in (("q", q, num_heads * dim), ("k", k, num_heads * dim), ("v", v, num_heads * vdim)):
+        _cuda(t, f"gated_attn {name}", q.dtype, contiguous=False)
+        _need(_rows(t, f"gated_attn {name}") == q.stride(0) and t.shape[1] == n and t.shape[0] == q.shape[0], f"gated_attn: {name} has the wrong shape or stride")
+    T = q.shape[0]
+    vcols = vdim + (1 if ext else 0)
+    _cuda(log_decay, "gated_attn log_decay", torch.float32)
+    per_channel = log_decay.numel() == T * num_heads * dim
+    _need(per_channel or log_decay.numel() == T * num_heads, f"gated_attn: log_decay {tuple(log_decay.shape)} is neither [T, H dim] nor [T, H]")
+    if in_scale is not None:
+        _cuda(in_scale, "gated_attn in_scale", torch.float32)
+        _need(in_scale.numel() == T * num_heads, "gated_attn: in_scale must be [T, H]")
+    _cuda(state, "gated_attn state", torch.float32)
+    _need(state.dim() == 4 and tuple(state.shape[1:]) == (num_heads, dim, vcols), f"gated_attn: state {tuple(state.shape)} is not [slots, {num_heads}, {dim}, {vcols}]")
+    _cuda(slot_ids, "gated_attn slot_ids", torch.int32)
+    _cuda(seq_start, "gated_attn seq_start", torch.int32)
+    S = slot_ids.numel()
+    _need(seq_start.numel() == S + 1, "gated_attn: seq_start must hold one more entry than there are sequences")
+    out = torch.empty((T, num_heads * vcols), dtype=torch.float32, device=q.device)
+    lib = build.load("gated_recurrent")
+    rc = lib.rl_gated_attn(
+        _p(q), _p(k), _p(v), c_int(_dt(q, "gated_attn")), c_int(q.stride(0)), _p(log_decay), c_int(1 if per_channel else 0), _p(in_scale),
+        c_float(q_scale), _p(state), _p(slot_ids), _p(seq_start), _p(out), c_int(out.stride(0)), c_int(S), c_int(num_heads), c_int(dim),
+        c_int(vdim), c_int(1 if ext else 0), _stream(),
+    )
+    _check(lib, rc, "gated_attn")
+    return out
+
+
+def gated_attn_chunked_takes(dim: int, vcols: int) -> bool:
+    """Whether the chunked form of `gated_attn` is built for these sizes."""
+    return False
+
+
+GATE_NONE, GATE_SIGMOID, GATE_SILU = 0, 1, 2
+
+
+def head_norm_gate(
+    x: torch.Tensor, num_heads: int, n: int, weight: Optional[torch.Tensor], eps: float, gate: Optional[torch.Tensor], gate_act: int,
+    act_dtype: torch.dtype, m: Optional[torch.Tensor] = None, den_eps: float = 0.0, out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Per (row, head): y = v / sqrt(mean(v^2) + eps) * weight * act(gate) * out_scale over the head's n values.
+
+    x: float32 [T, H xh] with xh = n, or n + 1 when m (float32 [T, H]) is given: the head's last number is then its n . q and
+    v = x / (max(|n . q|, exp(-m)) + den_eps).  weight: float32 [n] (shared by the heads), [H n] or None.  gate: [T, >= H n] rows of
+    `act_dtype` or None; gate_act: GATE_NONE (the gate itself), GATE_SIGMOID, GATE_SILU.  out: [T, H n] rows of `act_dtype`."""
+    _cuda(x, "head_norm_gate x", torch.float32, contiguous=False)
+    xs = _rows(x, "head_norm_gate x")
+    T = x.shape[0]
+    xh = n + (1 if m is not None else 0)
+    _need(x.shape[1] == num_heads * xh, f"head_norm_gate: x {tuple(x.shape)} is not [T, {num_heads} * {xh}]")
+    per_head = 0
+    if weight is not None:
+        _cuda(weight, "head_norm_gate weight", torch.float32)
+        _need(weight.numel() in (n, num_heads * n), "head_norm_gate: weight must hold n or H n numbers")
+        per_head = 1 if (weight.numel() == num_heads * n and num_heads > 1) else 0
+    if m is not None:
+        _cuda(m, "head_norm_gate m", torch.float32)
+        _need(m.numel() == T * num_heads, "head_norm_gate: m must be [T, H]")
+    gs = 0
+    if gate is not None:
+        _cuda(gate, "head_norm_gate gate", act_dtype, contiguous=False)
+        gs = _rows(gate, "head_norm_gate gate")
+        _need(gate.shape[0] == T and gate.shape[1] >= num_heads * n, "head_norm_gate: gate rows too short")
+    if out is None:
+        out = torch.empty((T, num_heads * n), dtype=act_dtype, device=x.device)
+    _cuda(out, "head_norm_gate out", act_dtype, contiguous=False)
+    _need(tuple(out.shape) == (T, num_heads * n) and _rows(out, "head_norm_gate out") >= num_heads * n, "head_norm_gate: out must be [T, H n]")
+    lib = build.load("gated_recurrent")
+    rc = lib.rl_head_norm_gate(
+        _p(x), c_int(xs), c_int(xh), _p(m), c_float(den_eps), _p(weight), c_int(per_head), c_float(eps), _p(gate), c_int(gs), c_int(gate_act),
+        c_float(out_scale), _p(out), c_int(out.stride(0)), c_int(_DT[act_dtype]), c_int(T), c_int(num_heads), c_int(n), _stream(),
+    )
+    _check(lib, rc, "head_norm_gate")
+    return out
+
 
 
 ACT_RELU2 = 1  # relu(x)^2

@@ -103,6 +103,9 @@ class Model:
         stream: ResidualStream = self.embedding.forward(step.tokens)
         for run, entry in enumerate(self.spec.schedule):
             block = self.blocks[entry.layer]
+            if entry.add_input:
+                # the embedding's rows once more, as a 32-bit term of the residual sum (the stream itself has moved on)
+                stream.add(self.embedding.forward(step.tokens).x.unsqueeze(0))
             source = run if entry.cache_from is None else entry.cache_from
             view = cache.view(source, tables) if cache.owns(source) else None
             block.forward(stream, step, view, shared_cache=entry.cache_from is not None)

@@ -42,7 +42,8 @@ def decode_splits(n_seqs: int, num_heads: int, num_kv_heads: int, kv_len: int, h
 
 
 _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight", "gate": "g", "sink": "sink", "head_mix": "talk",
-          "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias"}
+          "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias", "q_norm": "q_norm.weight",
+          "k_norm": "k_norm.weight"}
 
 
 @MIXERS.register("attention")
@@ -58,9 +59,14 @@ class Attention(Mixer):
     Optional params, each absent from a plain attention: value_dim (the size of a value head where it differs
     from head_dim), scale, sink (bool: exp(sink_h) joins the softmax's denominator), head_mix (bool: the heads' scaled
     scores are mixed by a learned [H, H] matrix before the softmax), gate (bool: the concatenated heads are multiplied
-    by sigmoid(Wg xn) before Wo), bias (bool: q, k, v and the output projection have biases), out_scale (a constant
-    factor on the result, applied in 32-bit where the heads' result is formed), names (tensor names after the prefix,
-    keys q k v o gate sink head_mix q_bias k_bias v_bias o_bias).
+    by sigmoid(Wg xn) before Wo), bias (bool: q, k, v and the output projection have biases; "qkv": only q, k, v),
+    out_scale (a constant factor on the result, applied in 32-bit where the heads' result is formed), sink "zero" (a sink
+    whose score is the constant 0: the softmax's denominator grows by one, no tensor), qk_norm (None, or the eps of an RMS norm
+    of every q and k head over the head's numbers, with one learned weight row for the q heads and one for the k heads, after
+    the biases and before the rotation), softcap (0, or the cap c of s <- c tanh(s / c) on the scaled scores), chunk (0, or the
+    size of the chunks, counted from position 0, outside of which a query sees nothing; the cache gives back the pages of
+    chunks that are over), names (tensor names after the prefix, keys q k v o gate sink head_mix q_bias k_bias v_bias o_bias
+    q_norm k_norm).
     tensors: <prefix>q_proj.weight [H hd, d], k_proj.weight [K hd, d], v_proj.weight [K vd, d],
              o_proj.weight [d, H vd]; with the options also g [H vd, d], sink [H], talk [H, H] and the biases.
              q, k, v (and the gate) are kept as one matrix so that one product
@@ -84,9 +90,17 @@ class Attention(Mixer):
         self.window = int(self._param("window"))
         self.vd = int(spec.params.get("value_dim") or self.hd)
         self.has_sink = bool(spec.params.get("sink", False))
+        self.zero_sink = spec.params.get("sink") == "zero"
+        qk_norm = spec.params.get("qk_norm")
+        self.qk_norm_eps = None if qk_norm is None else float(qk_norm)
+        self.softcap = float(spec.params.get("softcap", 0.0) or 0.0)
+        self.chunk = int(spec.params.get("chunk", 0) or 0)
+        if self.softcap < 0 or self.chunk < 0:
+            raise ConfigError(f"attention: softcap {self.softcap} and chunk {self.chunk} must not be negative")
         self.has_mix = bool(spec.params.get("head_mix", False))
         self.has_gate = bool(spec.params.get("gate", False))
         self.has_bias = bool(spec.params.get("bias", False))
+        self.has_o_bias = self.has_bias and spec.params.get("bias") != "qkv"
         self.out_scale = float(spec.params.get("out_scale", 1.0))
         self.names = dict(_NAMES, **dict(spec.params.get("names", {})))
         if min(self.H, self.K, self.hd, self.vd) <= 0 or self.H % self.K:
@@ -99,6 +113,7 @@ class Attention(Mixer):
         # what the kernels built for a plain attention take: equal key and value sizes, at most a sink beside the plain softmax
         # (the 32-bit attention kernel has none), and in bfloat16 a head size that moves in 16-byte pieces
         plain = self.vd == self.hd and not (self.has_mix or self.has_gate or self.has_bias) and self.out_scale == 1.0 and magnitude == 1.0
+        plain = plain and not (self.zero_sink or self.qk_norm_eps is not None or self.softcap or self.chunk)
         if plain and self.has_sink:
             plain = runtime.dtype != torch.float32 and self.hd % 8 == 0
         self.extended = not plain
@@ -119,11 +134,11 @@ class Attention(Mixer):
         self.qd, self.kvd, self.vvd, self.od = self.H * self.hd, self.K * self.hd, self.K * self.vd, self.H * self.vd
         self.w_qkv = None
         self.w_o = None
-        self.b_in = self.b_o = self.sink = self.mix = None
+        self.b_in = self.b_o = self.sink = self.mix = self.w_q_norm = self.w_k_norm = None
         self.fold_matrix = None  # what `fold_queries` mixes by in a decode step: the mixing matrix, or the identity
 
     def cache_need(self):
-        return KVNeed(self.K, self.hd, self.window, value_dim=self.vd if self.vd != self.hd else None)
+        return KVNeed(self.K, self.hd, self.window, value_dim=self.vd if self.vd != self.hd else None, chunk=self.chunk)
 
     def children(self):
         return (self.position,)
@@ -138,13 +153,17 @@ class Attention(Mixer):
         }
         if self.has_gate:
             infos[p + n["gate"]] = ParamInfo((self.od, self.d))
-        if self.has_sink:
+        if self.has_sink and not self.zero_sink:
             infos[p + n["sink"]] = ParamInfo((self.H,), "scalars")
+        if self.qk_norm_eps is not None:
+            infos[p + n["q_norm"]] = ParamInfo((self.hd,), "scalars", centre=1.0)
+            infos[p + n["k_norm"]] = ParamInfo((self.hd,), "scalars", centre=1.0)
         if self.has_mix:
             infos[p + n["head_mix"]] = ParamInfo((self.H, self.H), "scalars")
         if self.has_bias:
             for key, size in (("q_bias", self.qd), ("k_bias", self.kvd), ("v_bias", self.vvd), ("o_bias", self.d)):
-                infos[p + n[key]] = ParamInfo((size,), "scalars", centre=0.0)
+                if key != "o_bias" or self.has_o_bias:
+                    infos[p + n[key]] = ParamInfo((size,), "scalars", centre=0.0)
         return infos
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
@@ -154,13 +173,18 @@ class Attention(Mixer):
             parts.append(tensors[p + n["gate"]])
         self.w_qkv = torch.cat(parts, dim=0).contiguous()
         self.w_o = tensors[p + n["o"]].contiguous()
-        if self.has_sink:
+        if self.zero_sink:
+            self.sink = torch.zeros(self.H, dtype=torch.float32, device=self.w_o.device)
+        elif self.has_sink:
             self.sink = tensors[p + n["sink"]].contiguous()
+        if self.qk_norm_eps is not None:
+            self.w_q_norm, self.w_k_norm = tensors[p + n["q_norm"]].contiguous(), tensors[p + n["k_norm"]].contiguous()
         if self.has_mix:
             self.mix = tensors[p + n["head_mix"]].contiguous()
         if self.has_bias:
             self.b_in = torch.cat([tensors[p + n["q_bias"]], tensors[p + n["k_bias"]], tensors[p + n["v_bias"]]]).contiguous()
-            self.b_o = (tensors[p + n["o_bias"]] * self.out_scale).contiguous()
+            if self.has_o_bias:
+                self.b_o = (tensors[p + n["o_bias"]] * self.out_scale).contiguous()
 
     def output_bias(self):
         return self.b_o
@@ -176,11 +200,12 @@ class Attention(Mixer):
         inv_freq, rotary_dim, interleaved, magnitude = self.rotation
         ops.qkv_prep(
             proj, self.b_in, step.tok_pos, step.tok_seq, cache.block_table, cache.k_pages, cache.v_pages, inv_freq, magnitude,
-            self.H, self.K, self.hd, self.vd, rotary_dim, interleaved,
+            self.H, self.K, self.hd, self.vd, rotary_dim, interleaved, q_norm=self.w_q_norm, k_norm=self.w_k_norm,
+            norm_eps=self.qk_norm_eps or 0.0,
         )
         gate = proj[:, self.qd + self.kvd + self.vvd :] if self.has_gate else None
         parts = self.K if self.has_mix else 1
-        if (self.rt.dtype == torch.bfloat16 and ops.flash_mix_takes(self.hd, self.vd, parts) and proj.stride(0) % 8 == 0
+        if (self.rt.dtype == torch.bfloat16 and ops.flash_mix_takes(self.hd, self.vd, parts) and proj.stride(0) % 8 == 0 and not self.softcap and not self.chunk
                 and (out is None or (out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)) and (self.qd + self.kvd + self.vvd) % 2 == 0):
             if step.decode_only and ops.flash_mix_decode_takes(self.H, self.K, self.hd, self.vd):
                 # single tokens: all heads of a sequence are the rows of one block, which reads a key tile once for all of them;
@@ -208,7 +233,8 @@ class Attention(Mixer):
             return a, self.w_o
         a = ops.attn_ext(
             proj, cache.k_pages, cache.v_pages, cache.block_table, step.tok_seq, step.tok_pos, self.H, self.K, self.hd, self.vd,
-            self.scale, window=self.window, sink=self.sink, mix=self.mix, gate=gate, out_scale=self.out_scale, out=out,
+            self.scale, window=self.window, sink=self.sink, mix=self.mix, gate=gate, out_scale=self.out_scale, out=out, chunk=self.chunk,
+            softcap=self.softcap,
         )
         return a, self.w_o
 

@@ -99,6 +99,8 @@ class ParamInfo:
     shape: Tuple[int, ...]
     kind: str = "matrix"
     centre: Optional[float] = None
+    upper: Optional[int] = None  # of a "table" whose rows name different members of 0 .. upper - 1 (random models draw such rows)
+    free: int = 0  # a -1 in `shape` is a size that only the checkpoint names (the part reads it at load); random models use `free`
 
 
 def runtime_dtype(info: ParamInfo, stored: torch.dtype, run: torch.dtype) -> torch.dtype:
@@ -118,7 +120,9 @@ class KVNeed:
 
     values=False: the mixer keeps one row per position and head only (a latent from which it
     makes keys and values itself); the group then has no value pages.
-    value_dim: the size of a value row where it differs from a key row's `head_dim` (None: the same)."""
+    value_dim: the size of a value row where it differs from a key row's `head_dim` (None: the same).
+    chunk: 0, or the size of the chunks (counted from position 0) outside of which no query reads: the pages that lie wholly before
+    the chunk of the next position are given back."""
 
     num_kv_heads: int
     head_dim: int
@@ -126,6 +130,7 @@ class KVNeed:
     dtype: Optional[torch.dtype] = None  # None: the run's activation type
     values: bool = True
     value_dim: Optional[int] = None
+    chunk: int = 0
 
 
 @dataclass(frozen=True)
@@ -162,6 +167,12 @@ class Part:
             raise ConfigError(f"part '{self.spec.kind}' (prefix '{self.prefix}') lacks parameter '{key}'") from None
 
 
+class NormedTerms(list):
+    """What a mixer returns when its result is a sum of terms that each go through an RMS norm of their own:
+    a list of (delta, (weight, eps)), delta as `Mixer.forward` describes it; the result is sum_i rmsnorm(delta_i) * weight_i.
+    Constant factors of the terms are part of their weights."""
+
+
 class ResidualStream:
     """The 32-bit residual stream x[T, d] plus what was returned last and not yet added.
 
@@ -187,6 +198,17 @@ class ResidualStream:
             raise ConfigError("a sublayer's result with a bias row can only be added through a norm of that result")
         self.pending = delta
         self.pending_norm = None if norm is None else (norm[0], norm[1], bias)
+
+    def add_result(self, result, norm=None, bias: Optional[torch.Tensor] = None) -> None:
+        """`add` for what a sublayer returned: a tensor, or `NormedTerms`, whose terms are added one after the other (each but the
+        last by a pass of its own; the last stays pending for the next norm's kernel)."""
+        if isinstance(result, NormedTerms):
+            if norm is not None or bias is not None:
+                raise ConfigError("a sublayer's result that is a sum of normed terms takes no further norm or bias row")
+            for delta, term_norm in result:
+                self.add(delta, norm=term_norm)
+        else:
+            self.add(result, norm=norm, bias=bias)
 
     def take_pending(self):
         """(delta, norm) of what is pending, which is the caller's to add from now on."""
@@ -261,7 +283,7 @@ class Mixer(Part):
         return None
 
     def forward(self, xn: torch.Tensor, step, cache, shared_cache: bool = False) -> torch.Tensor:
-        """xn[T, d] -> delta [T, d] (or partial sums [parts, T, d]).
+        """xn[T, d] -> delta [T, d] (or partial sums [parts, T, d]), or `NormedTerms`.
 
         cache: this run's view of the cache (a KVView or StateView, or None).
         shared_cache: the view belongs to an earlier run of the schedule; read it, do not write it."""

@@ -36,12 +36,16 @@ class PreNormBlock(Block):
         xn = self.norms["mixer"].forward(stream)
         if self._folded(stream, xn, step, cache, shared_cache):
             return
-        stream.add(self.mixer.forward(xn, step, cache, shared_cache), bias=self.mixer.output_bias())
+        stream.add_result(self.mixer.forward(xn, step, cache, shared_cache), bias=self.mixer.output_bias())
+        if self.feed_forward is None:  # a layer may consist of its mixer alone
+            return
         xn = self.norms["feed_forward"].forward(stream)
         stream.add(self.feed_forward.forward(xn, step))
 
     def _folded(self, stream: ResidualStream, xn, step, cache, shared_cache: bool) -> bool:
         if not (step.decode_only and self.rt.dtype == torch.bfloat16 and xn.shape[0] <= STREAM_MAX_ROWS and xn.is_cuda and _fold_enabled()):
+            return False
+        if self.feed_forward is None:
             return False
         norm, gated = self.norms["feed_forward"].rms_weight(), self.feed_forward.gated_weights()
         if norm is None or gated is None or self.mixer.output_bias() is not None:
@@ -94,7 +98,7 @@ class SandwichBlock(Block):
 
     def forward(self, stream: ResidualStream, step, cache, shared_cache: bool = False) -> None:
         xn = self.norms["mixer"].forward(stream)
-        stream.add(self.mixer.forward(xn, step, cache, shared_cache), norm=self.norms["mixer_out"].rms_weight(), bias=self.mixer.output_bias())
+        stream.add_result(self.mixer.forward(xn, step, cache, shared_cache), norm=self.norms["mixer_out"].rms_weight(), bias=self.mixer.output_bias())
         if self.feed_forward is None:
             return
         xn = self.norms["feed_forward"].forward(stream)

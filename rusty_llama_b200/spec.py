@@ -44,10 +44,14 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.  `cache_from` names an earlier entry of the schedule
-    (by its index) whose cache this run reads instead of filling its own."""
+    (by its index) whose cache this run reads instead of filling its own.
+    `add_input`: the embedding's output (the stream as it was before the first run) is added to the stream before this
+    run, once, ahead of the run's first norm (a design that runs a stretch of layers several times and feeds every
+    pass but the first with its input again)."""
 
     layer: int
     cache_from: Optional[int] = None
+    add_input: bool = False
 
 
 @dataclass(frozen=True)

@@ -39,7 +39,7 @@ def compare_with_checkpoint(
         if name not in found:
             continue
         dtype, shape = found[name]
-        if tuple(shape) != tuple(info.shape):
+        if len(shape) != len(info.shape) or any(w not in (-1, h) for h, w in zip(shape, info.shape)):  # (-1: the checkpoint's to say)
             wrong_shape.append((name, tuple(shape), tuple(info.shape)))
         ok = dtype in (_INT_STORED if info.kind == "table" else _FLOAT_STORED)
         if not ok:

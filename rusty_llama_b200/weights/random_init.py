@@ -10,6 +10,7 @@ which tensors are made.
 
 from __future__ import annotations
 
+import dataclasses
 import hashlib
 import json
 import os
@@ -33,6 +34,8 @@ def _tensor_seed(seed: int, name: str) -> int:
 def random_tensor(name: str, info: ParamInfo, seed: int, dtype: torch.dtype, std: float, norm_jitter: float, device="cpu") -> torch.Tensor:
     gen = torch.Generator(device=device)
     gen.manual_seed(_tensor_seed(seed, name))
+    if any(n < 0 for n in info.shape):  # a size that only a checkpoint names: the part's choice for random models
+        info = dataclasses.replace(info, shape=tuple(info.free if n < 0 else n for n in info.shape))
     if info.centre is not None and info.kind in ("vector", "scalars"):
         # a tensor that says what its values lie around (a norm's distance from one, a bias): spread by the jitter, or a tenth
         t = info.centre + (norm_jitter or 0.1) * torch.randn(info.shape, generator=gen, dtype=torch.float32, device=device)
@@ -41,6 +44,10 @@ def random_tensor(name: str, info: ParamInfo, seed: int, dtype: torch.dtype, std
         if norm_jitter:
             t += norm_jitter * torch.randn(info.shape, generator=gen, dtype=torch.float32, device=device)
     elif info.kind == "table":
+        if info.upper and len(info.shape) == 2 and info.shape[1] <= info.upper:
+            # every row names different members of 0 .. upper - 1: the first places of a random order
+            keys = torch.rand((info.shape[0], info.upper), generator=gen, dtype=torch.float32, device=device)
+            return keys.argsort(dim=1)[:, : info.shape[1]].to(torch.int32).contiguous()
         return torch.zeros(info.shape, dtype=torch.int32, device=device)
     elif info.kind == "scalars":
         # learned numbers that enter 32-bit arithmetic directly: single rows (a sink, a bias, a norm of a latent) are
