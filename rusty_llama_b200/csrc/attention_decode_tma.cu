@@ -100,7 +100,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const float* __restrict__ inv_freq, int rot, int interleaved,
                        unsigned int* __restrict__ counters, bf16* __restrict__ out, int out_stride,
                        const float* __restrict__ q_parts, int n_parts, long long part_stride, int test_role,
-                       uint32_t test_ns, const float* __restrict__ sink) {
+                       uint32_t test_ns, const float* __restrict__ sink, int chunk, float softcap) {
   // all shared memory is dynamic, so that the ring starts at the block's first byte (1024-byte
   // aligned, as the 128-byte swizzle needs)
   constexpr int STAGES = Shape<HD>::STAGES, STAGE_BYTES = Shape<HD>::STAGE_BYTES, BOXES = Shape<HD>::BOXES;
@@ -143,7 +143,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   // writes the queries and the newest position's key and value, nothing else that is read here.
   const int kv_len = seq_len[s];
   const int pos = kv_len - 1;
-  const int first = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
+  const int first = rl_first_key(pos, window, chunk);
   const int tile_lo = first / PAGE, tile_hi = pos / PAGE;  // inclusive, in pages
   const int n_tiles = tile_hi - tile_lo + 1;
   const int per_split = (n_tiles + n_splits - 1) / n_splits;
@@ -397,7 +397,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      float v = s_acc[e] * scale_log2;
+      float v = rl_score_log2(s_acc[e], scale_log2, softcap);
       if (need_mask) {
         const int key = key0 + g + 8 * (e >> 1);
         if (key < first || key > pos) v = -INFINITY;
@@ -583,7 +583,7 @@ static int launch_decode_tma(const void* q, int q_stride, const void* k_pages, c
                              void* out, int out_stride, int n_seqs, int H, int K, int window, float scale, int n_splits,
                              int* status, int fuse, const float* inv_freq, int rot, int interleaved, unsigned int* counters,
                              const float* q_parts, int n_parts, long long part_stride, int wait_test_role,
-                             unsigned int wait_test_ns, const float* sink, cudaStream_t stream) {
+                             unsigned int wait_test_ns, const float* sink, int chunk, float softcap, cudaStream_t stream) {
   CUtensorMap map_k, map_v;
   if (make_page_map(&map_k, k_pages, n_pages, K, PAGE, HD, PAGE) || make_page_map(&map_v, v_pages, n_pages, K, PAGE, HD, PAGE))
     RL_REFUSE(10, "attn_decode_tma: cannot describe the cache pages to TMA");
@@ -597,7 +597,7 @@ static int launch_decode_tma(const void* q, int q_stride, const void* k_pages, c
                             table_width, seq_len, part_o, part_ml, H, K, window, scale * 1.4426950408889634f, n_splits, status,
                             fuse, (bf16*)const_cast<void*>(k_pages), (bf16*)const_cast<void*>(v_pages), inv_freq, fuse ? rot : 0,
                             interleaved, counters, (bf16*)out, out_stride, q_parts, n_parts, part_stride, wait_test_role,
-                            (uint32_t)wait_test_ns, sink));
+                            (uint32_t)wait_test_ns, sink, chunk, softcap));
   if (counters != nullptr) return 0;
   dim3 grid2(H, n_seqs);
   RL_LAUNCH_CHECK(rl_launch(attn_decode_merge_kernel, grid2, 128, 0, stream, (const float*)part_o, (const float*)part_ml,
@@ -611,7 +611,7 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
                               float scale, int n_splits, int* status, int fuse, const float* inv_freq, int rot,
                               int interleaved, unsigned int* counters, const float* q_parts, int n_parts,
                               long long part_stride, int wait_test_role, unsigned int wait_test_ns, const float* sink,
-                              cudaStream_t stream) {
+                              int chunk, float softcap, cudaStream_t stream) {
   if (n_seqs <= 0 || H <= 0 || K <= 0 || n_pages <= 0) RL_REFUSE(1, "attn_decode_tma: S=%d H=%d K=%d pages=%d", n_seqs, H, K, n_pages);
   if (!rl_attn_decode_tma_takes(hd)) RL_REFUSE(2, "attn_decode_tma: head size %d, this kernel is built for 64 and 128", hd);
   if (H % K) RL_REFUSE(3, "attn_decode_tma: %d query heads are not a multiple of %d kv heads", H, K);
@@ -619,7 +619,8 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
   if (q_stride % 8) RL_REFUSE(5, "attn_decode_tma: query row stride %d breaks 16-byte alignment", q_stride);
   if (((n_parts > 0 ? (uintptr_t)0 : (uintptr_t)q) | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) RL_REFUSE(6, "attn_decode_tma: operands must be 16-byte aligned");
   if (n_splits <= 0 || n_splits > 64 || n_seqs > 65535) RL_REFUSE(7, "attn_decode_tma: splits=%d (1..64) seqs=%d", n_splits, n_seqs);
-  if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "attn_decode_tma: bad window or scale, or no status word");
+  if (window < 0 || chunk < 0 || softcap < 0.f || status == nullptr || !(scale > 0.f))
+    RL_REFUSE(8, "attn_decode_tma: bad window, chunk, cap or scale, or no status word");
   if (fuse < 0 || fuse > 2 || rot < 0 || rot > hd || (rot & 7) || (fuse && rot > 0 && inv_freq == nullptr))
     RL_REFUSE(12, "attn_decode_tma: fuse=%d with a rotary size of %d (a multiple of 8 up to the head size)%s", fuse, rot, inv_freq ? "" : " and no angles");
   if (n_parts < 0 || n_parts > 64 || (n_parts > 0 && (q_parts == nullptr || fuse == 0 || ((uintptr_t)q_parts & 15) || part_stride % 4 || q_stride % 4)))
@@ -628,7 +629,7 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
 #define RL_DECODE_TMA(HDV)                                                                                                  \
   return launch_decode_tma<HDV>(q, q_stride, k_pages, v_pages, n_pages, block_table, table_width, seq_len, part_o, part_ml, out, \
                                 out_stride, n_seqs, H, K, window, scale, n_splits, status, fuse, inv_freq, rot, interleaved,      \
-                                counters, q_parts, n_parts, part_stride, wait_test_role, wait_test_ns, sink, stream)
+                                counters, q_parts, n_parts, part_stride, wait_test_role, wait_test_ns, sink, chunk, softcap, stream)
   if (hd == 64) RL_DECODE_TMA(64);
   RL_DECODE_TMA(128);
 #undef RL_DECODE_TMA

@@ -121,7 +121,7 @@ flash_mix_kernel(const bf16* __restrict__ q, long long q_row_stride, int q_head_
                  const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                  const int* __restrict__ seq_start, const int* __restrict__ seq_pos0, const float* __restrict__ sink,
                  const bf16* __restrict__ gate, int gate_stride, float out_scale, bf16* __restrict__ out, int out_stride, int H, int K,
-                 int kdim, int vdim, int window, float scale_log2) {
+                 int kdim, int vdim, int window, float scale_log2, int chunk, float softcap) {
   constexpr int STRIDE = HD + 8;  // 16 bytes of padding per row keep ldmatrix free of bank conflicts
   constexpr int KSTEPS = HD / 16;
   constexpr int NTHREADS = BM * 2;  // a warp per 16 query rows
@@ -154,7 +154,7 @@ flash_mix_kernel(const bf16* __restrict__ q, long long q_row_stride, int q_head_
   const int* table = block_table + (size_t)s * table_width;
   const int last_pos = pos0 + row0 + rows_here - 1;
   const int first_pos = pos0 + row0;
-  const int lowest_key = (window != 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
+  const int lowest_key = rl_first_key(first_pos, window, chunk);
   const int tile_lo = lowest_key / BN, tile_hi = last_pos / BN;
   const int per_tile = parts + 1;
   const int n_loads = (tile_hi - tile_lo + 1) * per_tile;
@@ -184,6 +184,7 @@ flash_mix_kernel(const bf16* __restrict__ q, long long q_row_stride, int q_head_
     l_run[0] = l_run[1] = (t4 == 0) ? 1.f : 0.f;
   }
   const int qpos[2] = {first_pos + warp * 16 + g, first_pos + warp * 16 + g + 8};
+  const int qlow[2] = {rl_first_key(qpos[0], window, chunk), rl_first_key(qpos[1], window, chunk)};
   float s_acc[BN / 8][4];
 
   for (int n = 0; n < n_loads; ++n) {
@@ -221,9 +222,9 @@ flash_mix_kernel(const bf16* __restrict__ q, long long q_row_stride, int q_head_
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int r = e >> 1;
-          float v = s_acc[nn][e] * scale_log2;
+          float v = rl_score_log2(s_acc[nn][e], scale_log2, softcap);
           const int key = key0 + nn * 8 + 2 * t4 + (e & 1);
-          const bool seen = key <= qpos[r] && (window == 0 || qpos[r] - key < window);
+          const bool seen = key <= qpos[r] && key >= qlow[r];
           if (!seen) v = -INFINITY;
           s_acc[nn][e] = v;
           tile_max[r] = fmaxf(tile_max[r], v);
@@ -310,7 +311,7 @@ template <int HD, int BM>
 static int launch_mix_rows(const bf16* q, long long q_row_stride, int q_head_stride, int parts, const bf16* k_pages, const bf16* v_pages,
                       const int* block_table, int table_width, const int* seq_start, const int* seq_pos0, const float* sink,
                       const bf16* gate, int gate_stride, float out_scale, bf16* out, int out_stride, int n_seqs, int max_q_len, int H, int K,
-                      int kdim, int vdim, int window, float scale, cudaStream_t stream) {
+                      int kdim, int vdim, int window, float scale, int chunk, float softcap, cudaStream_t stream) {
   const size_t smem = (size_t)(NBUF * BN + parts * BM) * (HD + 8) * sizeof(bf16);
   auto kern = flash_mix_kernel<HD, BM>;
   if (smem > 227 * 1024) RL_REFUSE(8, "flash_mix: %zu bytes of shared memory for %d query parts exceed the SM's", smem, parts);
@@ -321,7 +322,7 @@ static int launch_mix_rows(const bf16* q, long long q_row_stride, int q_head_str
   dim3 grid(H * n_seqs, (max_q_len + BM - 1) / BM);
   kern<<<grid, BM * 2, smem, stream>>>(q, q_row_stride, q_head_stride, parts, k_pages, v_pages, block_table, table_width, seq_start,
                                          seq_pos0, sink, gate, gate_stride, out_scale, out, out_stride, H, K, kdim, vdim, window,
-                                         scale * 1.4426950408889634f);
+                                         scale * 1.4426950408889634f, chunk, softcap);
   RL_LAUNCH_RESULT();
 }
 
@@ -329,7 +330,7 @@ template <int HD>
 static int launch_mix(const bf16* q, long long q_row_stride, int q_head_stride, int parts, const bf16* k_pages, const bf16* v_pages,
                       const int* block_table, int table_width, const int* seq_start, const int* seq_pos0, const float* sink,
                       const bf16* gate, int gate_stride, float out_scale, bf16* out, int out_stride, int n_seqs, int max_q_len, int H, int K,
-                      int kdim, int vdim, int window, float scale, cudaStream_t stream) {
+                      int kdim, int vdim, int window, float scale, int chunk, float softcap, cudaStream_t stream) {
   // 128 rows to a block where several query parts would leave one block of 64 rows alone on its SM anyway and the step has
   // the rows to fill it
   const size_t smem128 = (size_t)(NBUF * BN + parts * 128) * (HD + 8) * sizeof(bf16);
@@ -337,9 +338,9 @@ static int launch_mix(const bf16* q, long long q_row_stride, int q_head_stride, 
   if (HD <= 128 && parts > 1 && max_q_len > 64 && smem128 <= 227 * 1024 && 2 * smem64 > 227 * 1024)
     return launch_mix_rows<HD, 128>(q, q_row_stride, q_head_stride, parts, k_pages, v_pages, block_table, table_width, seq_start, seq_pos0,
                                     sink, gate, gate_stride, out_scale, out, out_stride, n_seqs, max_q_len, H, K, kdim, vdim, window, scale,
-                                    stream);
+                                    chunk, softcap, stream);
   return launch_mix_rows<HD, 64>(q, q_row_stride, q_head_stride, parts, k_pages, v_pages, block_table, table_width, seq_start, seq_pos0, sink,
-                                 gate, gate_stride, out_scale, out, out_stride, n_seqs, max_q_len, H, K, kdim, vdim, window, scale, stream);
+                                 gate, gate_stride, out_scale, out, out_stride, n_seqs, max_q_len, H, K, kdim, vdim, window, scale, chunk, softcap, stream);
 }
 
 // q: the queries [T][..], row stride q_row_stride, head h at h * q_head_stride, part p of a head at + p * kdim.
@@ -347,7 +348,7 @@ static int launch_mix(const bf16* q, long long q_row_stride, int q_head_stride, 
 RL_API int rl_flash_mix(const void* q, long long q_row_stride, int q_head_stride, int parts, const void* k_pages, const void* v_pages,
                         const int* block_table, int table_width, const int* seq_start, const int* seq_pos0, const float* sink,
                         const void* gate, int gate_stride, float out_scale, void* out, int out_stride, int n_seqs, int max_q_len, int H,
-                        int K, int kdim, int vdim, int page_size, int window, float scale, cudaStream_t stream) {
+                        int K, int kdim, int vdim, int page_size, int window, float scale, int chunk, float softcap, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0 || H <= 0 || K <= 0 || kdim <= 0 || vdim <= 0)
     RL_REFUSE(1, "flash_mix: S=%d max_q=%d H=%d K=%d kdim=%d vdim=%d", n_seqs, max_q_len, H, K, kdim, vdim);
   if (H % K) RL_REFUSE(2, "flash_mix: %d query heads are not a multiple of %d kv heads", H, K);
@@ -357,12 +358,13 @@ RL_API int rl_flash_mix(const void* q, long long q_row_stride, int q_head_stride
       ((uintptr_t)out | (uintptr_t)gate) % 4)
     RL_REFUSE(5, "flash_mix: strides or addresses break the alignment of 16-byte copies and paired stores");
   if ((long long)H * n_seqs > 0x7fffffffLL || max_q_len / 16 > 65535) RL_REFUSE(6, "flash_mix: the grid is too large");
-  if (window < 0 || (parts != 1 && parts != K)) RL_REFUSE(7, "flash_mix: window %d, parts %d of %d kv heads", window, parts, K);
+  if (window < 0 || chunk < 0 || softcap < 0.f || (parts != 1 && parts != K))
+    RL_REFUSE(7, "flash_mix: window %d, chunk %d, cap %g, parts %d of %d kv heads", window, chunk, (double)softcap, parts, K);
   const int hd = kdim > vdim ? kdim : vdim;
 #define RL_MIX(HDV)                                                                                                                   \
   return launch_mix<HDV>((const bf16*)q, q_row_stride, q_head_stride, parts, (const bf16*)k_pages, (const bf16*)v_pages, block_table,  \
                          table_width, seq_start, seq_pos0, sink, (const bf16*)gate, gate_stride, out_scale, (bf16*)out, out_stride,      \
-                         n_seqs, max_q_len, H, K, kdim, vdim, window, scale, stream)
+                         n_seqs, max_q_len, H, K, kdim, vdim, window, scale, chunk, softcap, stream)
   if (hd <= 32) RL_MIX(32);
   if (hd <= 64) RL_MIX(64);
   if (hd <= 128) RL_MIX(128);
@@ -382,7 +384,7 @@ template <int HD>
 __global__ void flash_mix_decode_kernel(const bf16* __restrict__ qf, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_pos0,
                                         const float* __restrict__ sink, float* __restrict__ part_o, float* __restrict__ part_ml, int H,
-                                        int K, int kdim, int vdim, int window, float scale_log2, int n_splits) {
+                                        int K, int kdim, int vdim, int window, float scale_log2, int n_splits, int chunk, float softcap) {
   constexpr int STRIDE = HD + 8;
   constexpr int KSTEPS = HD / 16;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -394,7 +396,7 @@ __global__ void flash_mix_decode_kernel(const bf16* __restrict__ qf, const bf16*
   const int g = lane >> 2, t4 = lane & 3;
   const int rep = H / K;
   const int pos = seq_pos0[s];  // the token's own position; its key and value are in the cache already
-  const int first = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
+  const int first = rl_first_key(pos, window, chunk);
   const int tile_first = first / BN, n_tiles = pos / BN - tile_first + 1;
   const int per = (n_tiles + n_splits - 1) / n_splits;
   const int tile_lo = tile_first + split * per, tile_hi = min(tile_first + n_tiles, tile_lo + per) - 1;
@@ -489,7 +491,7 @@ __global__ void flash_mix_decode_kernel(const bf16* __restrict__ qf, const bf16*
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int key = key0 + nn * 8 + 2 * t4 + (e & 1);
-              float v = s_acc[nn][e] * scale_log2;
+              float v = rl_score_log2(s_acc[nn][e], scale_log2, softcap);
               if (key > pos || key < first) v = -INFINITY;
               s_acc[nn][e] = v;
               tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
@@ -603,7 +605,7 @@ template <int HD>
 static int launch_mix_decode(const bf16* qf, const bf16* k_pages, const bf16* v_pages, const int* block_table, int table_width,
                              const int* seq_pos0, const float* sink, const bf16* gate, int gate_stride, float out_scale, float* part_o,
                              float* part_ml, bf16* out, int out_stride, int n_seqs, int H, int K, int kdim, int vdim, int window, float scale,
-                             int n_splits, cudaStream_t stream) {
+                             int n_splits, int chunk, float softcap, cudaStream_t stream) {
   const int warps = (H + 15) / 16;
   const size_t smem = (size_t)(NBUF * BN + K * warps * 16) * (HD + 8) * sizeof(bf16);
   auto kern = flash_mix_decode_kernel<HD>;
@@ -612,7 +614,7 @@ static int launch_mix_decode(const bf16* qf, const bf16* k_pages, const bf16* v_
     RL_REFUSE(8, "flash_mix_decode: cannot get %zu bytes of shared memory", smem);
   dim3 grid(n_splits, n_seqs);
   kern<<<grid, warps * 32, smem, stream>>>(qf, k_pages, v_pages, block_table, table_width, seq_pos0, sink, part_o, part_ml, H, K, kdim, vdim,
-                                           window, scale * 1.4426950408889634f, n_splits);
+                                           window, scale * 1.4426950408889634f, n_splits, chunk, softcap);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     snprintf(rl_error_buf, sizeof(rl_error_buf), "%s", cudaGetErrorString(e));
@@ -633,19 +635,20 @@ RL_API int rl_flash_mix_decode_smem(int H, int K, int hd_max) {
 RL_API int rl_flash_mix_decode(const void* qf, const void* k_pages, const void* v_pages, const int* block_table, int table_width,
                                const int* seq_pos0, const float* sink, const void* gate, int gate_stride, float out_scale, float* part_o,
                                float* part_ml, void* out, int out_stride, int n_seqs, int H, int K, int kdim, int vdim, int page_size,
-                               int window, float scale, int n_splits, cudaStream_t stream) {
+                               int window, float scale, int n_splits, int chunk, float softcap, cudaStream_t stream) {
   if (n_seqs <= 0 || H <= 0 || K <= 0 || kdim <= 0 || vdim <= 0 || n_splits <= 0 || !part_o || !part_ml)
     RL_REFUSE(1, "flash_mix_decode: S=%d H=%d K=%d kdim=%d vdim=%d splits=%d", n_seqs, H, K, kdim, vdim, n_splits);
   if (H % K || H > 256) RL_REFUSE(2, "flash_mix_decode: %d heads on %d kv heads (at most 256 heads)", H, K);
   if (page_size != BN) RL_REFUSE(3, "flash_mix_decode: page size %d, this kernel is built for %d", page_size, BN);
   if (kdim % 8 || vdim % 8) RL_REFUSE(4, "flash_mix_decode: key and value sizes %d / %d must be multiples of 8", kdim, vdim);
   if (((uintptr_t)qf | (uintptr_t)k_pages | (uintptr_t)v_pages) % 16) RL_REFUSE(5, "flash_mix_decode: addresses break the alignment of 16-byte copies");
-  if (window < 0 || n_seqs > 65535) RL_REFUSE(6, "flash_mix_decode: window %d, %d sequences", window, n_seqs);
+  if (window < 0 || chunk < 0 || softcap < 0.f || n_seqs > 65535)
+    RL_REFUSE(6, "flash_mix_decode: window %d, chunk %d, cap %g, %d sequences", window, chunk, (double)softcap, n_seqs);
   const int hd = kdim > vdim ? kdim : vdim;
 #define RL_MIXD(HDV)                                                                                                                    \
   return launch_mix_decode<HDV>((const bf16*)qf, (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_width, seq_pos0, sink,    \
                                 (const bf16*)gate, gate_stride, out_scale, part_o, part_ml, (bf16*)out, out_stride, n_seqs, H, K, kdim,    \
-                                vdim, window, scale, n_splits, stream)
+                                vdim, window, scale, n_splits, chunk, softcap, stream)
   if (hd <= 32) RL_MIXD(32);
   if (hd <= 64) RL_MIXD(64);
   if (hd <= 128) RL_MIXD(128);

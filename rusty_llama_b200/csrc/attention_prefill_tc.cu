@@ -201,7 +201,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ seq_start, const int* __restrict__ seq_pos0, bf16* __restrict__ out,
                         int out_stride, int H, int K, int window, float scale_log2, int* __restrict__ status,
-                        int test_role, uint32_t test_ns, const float* __restrict__ sink) {
+                        int test_role, uint32_t test_ns, const float* __restrict__ sink, int chunk, float softcap) {
   // All shared memory is dynamic, so that the tiles start at the block's first byte (1024-byte
   // aligned, as the 128-byte swizzle needs) and the small items fit behind them.
   constexpr int SUBS = HD / 64, Q_BYTES = SUBS * SUBQ_BYTES, KV_BYTES = SUBS * SUBK_BYTES;
@@ -239,7 +239,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int kh = h / (H / K);
   const int rows_here = min(BMQ, q_len - row0);
   const int first_pos = pos0 + row0, last_pos = first_pos + rows_here - 1;
-  const int lowest_key = (window != 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
+  const int lowest_key = rl_first_key(first_pos, window, chunk);
   const int tile_lo = lowest_key / BNK, tile_hi = last_pos / BNK;
   const int n_tiles = tile_hi - tile_lo + 1;
 
@@ -374,6 +374,10 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     // ---------------- softmax and output: warp w owns tensor-memory lanes 32 w .. 32 w + 31, one thread a query row
     const int r = warp * 32 + lane;
     const int qpos = first_pos + r;
+    const int qlow = rl_first_key(qpos, window, chunk);
+    // with a cap c the scores become tanh(raw * scale / c) first, and c log2(e) takes the scale's place from there on
+    const float exp_scale = softcap != 0.f ? softcap * 1.4426950408889634f : scale_log2;
+    const float cap_in = softcap != 0.f ? scale_log2 / exp_scale : 0.f;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
     const uint32_t o_addr = lane_addr + O_COL;
     float m_run = -INFINITY, l_run = 0.f;   // m_run in units of raw scores times scale_log2
@@ -400,7 +404,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
       tc_fence_after();
       const int key0 = (tile_lo + j) * BNK;
-      const bool need_mask = key0 + BNK - 1 > first_pos || window != 0;
+      const bool need_mask = key0 + BNK - 1 > first_pos || window != 0 || chunk != 0;
       const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) * BNK);
       // this thread's row of S in one round trip
       uint32_t v[BNK];
@@ -409,12 +413,16 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tmem_ld_wait();
       // (four running maxima and, below, four running sums: one chain of 64 dependent operations would leave the
       // few warps of an SM waiting on their own arithmetic)
+      if (softcap != 0.f) {
+#pragma unroll
+        for (int i = 0; i < BNK; ++i) v[i] = __float_as_uint(tanhf(__uint_as_float(v[i]) * cap_in));
+      }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < BNK; ++i) {
           const int key = key0 + i;
-          if (key > qpos || (window != 0 && qpos - key >= window)) v[i] = __float_as_uint(-INFINITY);
+          if (key > qpos || key < qlow) v[i] = __float_as_uint(-INFINITY);
           mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
         }
       } else {
@@ -422,7 +430,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int i = 0; i < BNK; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
       }
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      mx *= scale_log2;   // the scale is positive: the maximum commutes with it
+      mx *= exp_scale;   // the scale is positive: the maximum commutes with it
       // raise the running maximum only when it pays (see the header); the first tile sets it
       const bool raise = mx > m_run + RESCALE_THRESHOLD || (m_run == -INFINITY && mx != -INFINITY);
       const float m_next = raise ? mx : m_run;
@@ -455,8 +463,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < BNK / 2; ++i) {
-        const float p0 = exp2_fast(fmaf(__uint_as_float(v[2 * i]), scale_log2, neg_m));
-        const float p1 = exp2_fast(fmaf(__uint_as_float(v[2 * i + 1]), scale_log2, neg_m));
+        const float p0 = exp2_fast(fmaf(__uint_as_float(v[2 * i]), exp_scale, neg_m));
+        const float p1 = exp2_fast(fmaf(__uint_as_float(v[2 * i + 1]), exp_scale, neg_m));
         sum4[i & 3] += p0 + p1;
         pk[i] = pack2(p0, p1);
       }
@@ -515,7 +523,7 @@ template <int HD>
 static int launch_flash_tc(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages, int n_pages,
                            const int* block_table, int table_width, const int* seq_start, const int* seq_pos0, void* out,
                            int out_stride, int n_seqs, int max_q_len, int H, int K, int window, float scale, int* status,
-                           int wait_test_role, unsigned int wait_test_ns, const float* sink, cudaStream_t stream) {
+                           int wait_test_role, unsigned int wait_test_ns, const float* sink, int chunk, float softcap, cudaStream_t stream) {
   CUtensorMap map_q, map_k, map_v;
   if (make_matrix_map(&map_q, q, n_tokens, q_stride, q_stride, BMQ))
     RL_REFUSE(10, "flash_prefill_tc: cannot describe the query tensor to TMA");
@@ -528,7 +536,7 @@ static int launch_flash_tc(const void* q, int q_stride, int n_tokens, const void
   dim3 grid(H * n_seqs, (max_q_len + BMQ - 1) / BMQ);
   RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_q, map_k, map_v, block_table, table_width, seq_start, seq_pos0,
                             (bf16*)out, out_stride, H, K, window, scale * 1.4426950408889634f, status, wait_test_role,
-                            (uint32_t)wait_test_ns, sink));
+                            (uint32_t)wait_test_ns, sink, chunk, softcap));
   return 0;
 }
 
@@ -542,7 +550,7 @@ RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const 
                                int n_pages, const int* block_table, int table_width, const int* seq_start,
                                const int* seq_pos0, void* out, int out_stride, int n_seqs, int max_q_len, int H, int K,
                                int hd, int page_size, int window, float scale, int* status, int wait_test_role,
-                               unsigned int wait_test_ns, const float* sink, cudaStream_t stream) {
+                               unsigned int wait_test_ns, const float* sink, int chunk, float softcap, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0 || H <= 0 || K <= 0 || n_tokens <= 0 || n_pages <= 0)
     RL_REFUSE(1, "flash_prefill_tc: S=%d max_q=%d H=%d K=%d T=%d pages=%d", n_seqs, max_q_len, H, K, n_tokens, n_pages);
   if (!rl_flash_prefill_tc_takes(hd)) RL_REFUSE(2, "flash_prefill_tc: head size %d, this kernel is built for 64 and 128", hd);
@@ -552,10 +560,11 @@ RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const 
   if (((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) RL_REFUSE(6, "flash_prefill_tc: operands must be 16-byte aligned");
   if ((long long)H * n_seqs > 0x7fffffffLL || (max_q_len + BMQ - 1) / BMQ > 65535)
     RL_REFUSE(7, "flash_prefill_tc: H=%d x S=%d blocks or %d query rows exceed the grid", H, n_seqs, max_q_len);
-  if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "flash_prefill_tc: bad window or scale, or no status word");
+  if (window < 0 || chunk < 0 || softcap < 0.f || status == nullptr || !(scale > 0.f))
+    RL_REFUSE(8, "flash_prefill_tc: bad window, chunk, cap or scale, or no status word");
   if (hd == 64)
     return launch_flash_tc<64>(q, q_stride, n_tokens, k_pages, v_pages, n_pages, block_table, table_width, seq_start, seq_pos0, out,
-                               out_stride, n_seqs, max_q_len, H, K, window, scale, status, wait_test_role, wait_test_ns, sink, stream);
+                               out_stride, n_seqs, max_q_len, H, K, window, scale, status, wait_test_role, wait_test_ns, sink, chunk, softcap, stream);
   return launch_flash_tc<128>(q, q_stride, n_tokens, k_pages, v_pages, n_pages, block_table, table_width, seq_start, seq_pos0, out,
-                              out_stride, n_seqs, max_q_len, H, K, window, scale, status, wait_test_role, wait_test_ns, sink, stream);
+                              out_stride, n_seqs, max_q_len, H, K, window, scale, status, wait_test_role, wait_test_ns, sink, chunk, softcap, stream);
 }

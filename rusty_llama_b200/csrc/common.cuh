@@ -129,6 +129,22 @@ __device__ __forceinline__ float unary_post(float v, float code) {
   return v;
 }
 
+// The lowest key that a query at `pos` sees: `window` 0 or how many of the last positions it sees, `chunk` 0 or the size of
+// the chunks (counted from position 0) outside of which it sees nothing.
+__device__ __forceinline__ int rl_first_key(int pos, int window, int chunk) {
+  int first = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
+  if (chunk != 0) first = max(first, pos - pos % chunk);
+  return first;
+}
+
+// A raw score q . k as an exponent of two: raw * scale_log2 (scale_log2 = scale * log2 e), or with a cap c on the scaled
+// score, c tanh(raw * scale / c) * log2 e.
+__device__ __forceinline__ float rl_score_log2(float raw, float scale_log2, float softcap) {
+  if (softcap == 0.f) return raw * scale_log2;
+  const float cap_log2 = softcap * 1.4426950408889634f;
+  return cap_log2 * tanhf(raw * (scale_log2 / cap_log2));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -229,6 +229,343 @@ RL_API int rl_gated_attn(const void* q, const void* k, const void* v, int dtype,
   return 0;
 }
 
+// ---------------------------------------------------------------- the same recurrence, chunk by chunk
+// For prompts.  A sequence's tokens are cut into chunks of GC; with n tokens in a chunk, S the state before it,
+// A_i = sum_{l <= i} log a_l (per key channel, inside the chunk) and k'_j = b_j k_j:
+//   U      = sum_j diag(exp(A_(n-1) - A_j)) k'_j v_j^T                                  (1) what the chunk adds, every chunk at once
+//   S_next = diag(exp(A_(n-1))) S + U                                                    (2) the states before every chunk, chunk after chunk
+//   o_i    = S^T (q_i * exp(A_i)) + sum_{j<=i} (sum_r q_i[r] k'_j[r] exp(A_i[r] - A_j[r])) v_j   (3) the outputs, every chunk at once
+// Only exponents <= 0 occur, whatever the decays are: the scores of (3) between tokens of the same sub-chunk of 16 take
+// exp(A_i - A_j) channel by channel; between sub-chunks I > J they factor through the sub-chunks' borders,
+//   exp(A_i - A_(16 I - 1)) * exp(A_(16 I - 1) - A_(16 J + 15)) * exp(A_(16 J + 15) - A_j),
+// a factor of the query, one of the border pair and one of the key.  All of it is 32-bit FMA arithmetic over a scratch of one
+// [dim, vcols] matrix and one row of dim decays per (sequence, head, chunk).  The order of the sums differs from the
+// token-by-token kernel's and depends on where the chunks fall, so 32-bit runs keep to the other kernel.
+#define GC 64       // tokens per chunk
+#define GC_SUB 16   // tokens per sub-chunk
+#define GC_COLS 64  // state columns per block
+#define GR_LOG2E 1.4426950408889634f
+
+__device__ __forceinline__ float gr_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// (1): grid (S * H, chunks, column tiles), 256 threads: thread (ty, tx) owns rows ty + 16 a and columns 4 tx .. 4 tx + 3.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_chunk_state_kernel(const T* __restrict__ k, const T* __restrict__ v, int in_stride, const float* __restrict__ log_decay,
+                         int per_channel, const float* __restrict__ in_scale, const int* __restrict__ seq_start,
+                         float* __restrict__ scratch, float* __restrict__ chunk_decay, int max_chunks, int H, int dim, int vdim, int ext) {
+  extern __shared__ float sm[];
+  pdl_trigger();
+  pdl_wait();
+  const int s = blockIdx.x / H, h = blockIdx.x % H, c = blockIdx.y, col0 = blockIdx.z * GC_COLS;
+  const int vcols = vdim + ext;
+  const int t0 = seq_start[s] + c * GC;
+  const int n = min(GC, seq_start[s + 1] - t0);
+  if (n <= 0) return;
+  float* k_s = sm;             // [GC][dim]: first the decays' logarithms, then the weighted keys
+  float* v_s = sm + GC * dim;  // [GC][GC_COLS]
+  for (int idx = threadIdx.x; idx < n * dim; idx += 256) {
+    const int i = idx / dim, r = idx - i * dim;
+    const size_t th = (size_t)(t0 + i) * H + h;
+    k_s[idx] = GR_LOG2E * (per_channel ? log_decay[th * dim + r] : log_decay[th]);
+  }
+  for (int idx = threadIdx.x; idx < n * GC_COLS; idx += 256) {
+    const int i = idx / GC_COLS, cc = col0 + (idx - i * GC_COLS);
+    float vv = 0.f;
+    if (cc < vdim) vv = to_f32(v[(size_t)(t0 + i) * in_stride + (size_t)h * vdim + cc]);
+    else if (cc < vcols) vv = 1.f;
+    v_s[idx] = vv;
+  }
+  __syncthreads();
+  // per channel: what the tokens after token i still take away, and the whole chunk's decay
+  for (int r = threadIdx.x; r < dim; r += 256) {
+    float after = 0.f;
+    for (int i = n - 1; i >= 0; --i) {
+      const float la = k_s[i * dim + r];
+      k_s[i * dim + r] = after;
+      after += la;
+    }
+    if (blockIdx.z == 0) chunk_decay[((size_t)blockIdx.x * max_chunks + c) * dim + r] = gr_exp2(after);
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < n * dim; idx += 256) {
+    const int i = idx / dim, r = idx - i * dim;
+    const float b = in_scale ? in_scale[(size_t)(t0 + i) * H + h] : 1.f;
+    k_s[idx] = to_f32(k[(size_t)(t0 + i) * in_stride + (size_t)h * dim + r]) * b * gr_exp2(k_s[idx]);
+  }
+  __syncthreads();
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  float* u = scratch + ((size_t)blockIdx.x * max_chunks + c) * dim * vcols;
+  for (int r0 = 0; r0 < dim; r0 += 128) {  // 128 rows of the state at a time: eight to a thread
+    float acc[8][4];
+#pragma unroll
+    for (int a = 0; a < 8; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
+    for (int i = 0; i < n; ++i) {
+      const float4 vv = *reinterpret_cast<const float4*>(v_s + i * GC_COLS + 4 * tx);
+#pragma unroll
+      for (int a = 0; a < 8; ++a) {
+        const int r = r0 + ty + 16 * a;
+        if (r < dim) {
+          const float kv = k_s[i * dim + r];
+          acc[a][0] += kv * vv.x;
+          acc[a][1] += kv * vv.y;
+          acc[a][2] += kv * vv.z;
+          acc[a][3] += kv * vv.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < 8; ++a) {
+      const int r = r0 + ty + 16 * a;
+      if (r < dim) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = col0 + 4 * tx + e;
+          if (col < vcols) u[(size_t)r * vcols + col] = acc[a][e];
+        }
+      }
+    }
+  }
+}
+
+// (2): one thread per element of a (sequence, head)'s state; leaves in every chunk's place the state BEFORE that chunk.
+__global__ void gated_chunk_scan_kernel(float* __restrict__ state, const int* __restrict__ slot_ids, const int* __restrict__ seq_start,
+                                        float* __restrict__ scratch, const float* __restrict__ chunk_decay, int max_chunks, int H,
+                                        int dim, int vcols) {
+  pdl_trigger();
+  pdl_wait();
+  const int s = blockIdx.x / H, h = blockIdx.x % H;
+  const int elems = dim * vcols;
+  const int e = blockIdx.y * blockDim.x + threadIdx.x;
+  if (e >= elems) return;
+  const int r = e / vcols;
+  const int len = seq_start[s + 1] - seq_start[s];
+  float* st = state + ((size_t)slot_ids[s] * H + h) * elems + e;
+  float* u = scratch + (size_t)blockIdx.x * max_chunks * elems + e;
+  const float* g = chunk_decay + (size_t)blockIdx.x * max_chunks * dim + r;
+  float S = *st;
+  const int n_chunks = (len + GC - 1) / GC;
+  for (int c0 = 0; c0 < n_chunks; c0 += 8) {  // eight chunks' additions are asked for at once, then taken in order
+    float add[8], dec[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (c0 + j < n_chunks) {
+        add[j] = __ldcg(u + (size_t)(c0 + j) * elems);
+        dec[j] = __ldcg(g + (size_t)(c0 + j) * dim);
+      }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (c0 + j < n_chunks) {
+        u[(size_t)(c0 + j) * elems] = S;
+        S = dec[j] * S + add[j];
+      }
+  }
+  *st = S;
+}
+
+// (3): grid as (1).  Thread (ty, tx): scores P[ty + 16 a][tx + 16 b] (a, b: the sub-chunks of the query and of the key), then
+// outputs for rows ty + 16 a and columns 4 tx .. 4 tx + 3.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int in_stride,
+                       const float* __restrict__ log_decay, int per_channel, const float* __restrict__ in_scale, float q_scale,
+                       const int* __restrict__ seq_start, const float* __restrict__ scratch, int max_chunks, float* __restrict__ out,
+                       int out_stride, int H, int dim, int vdim, int ext) {
+  extern __shared__ float sm[];
+  pdl_trigger();
+  pdl_wait();
+  const int s = blockIdx.x / H, h = blockIdx.x % H, c = blockIdx.y, col0 = blockIdx.z * GC_COLS;
+  const int vcols = vdim + ext;
+  const int t0 = seq_start[s] + c * GC;
+  const int n = min(GC, seq_start[s + 1] - t0);
+  if (n <= 0) return;
+  const int DS = dim + 1;  // rows one apart in the banks
+  float* q_s = sm;                    // [GC][DS]
+  float* k_s = q_s + GC * DS;         // [GC][DS]
+  float* a_s = k_s + GC * DS;         // [GC][DS]: A_i in units of log 2
+  float* v_s = a_s + GC * DS;         // [GC][GC_COLS]
+  float* p_s = v_s + GC * GC_COLS;    // [GC][GC + 1]
+  float* d_s = p_s + GC * (GC + 1);   // [2][dim]: the decay over sub-chunk 1 and over sub-chunk 2
+  for (int idx = threadIdx.x; idx < GC * dim; idx += 256) {
+    const int i = idx / dim, r = idx - i * dim;
+    float qv = 0.f, kv = 0.f, la = 0.f;
+    if (i < n) {
+      const size_t at = (size_t)(t0 + i) * in_stride + (size_t)h * dim + r;
+      const size_t th = (size_t)(t0 + i) * H + h;
+      qv = to_f32(q[at]) * q_scale;
+      kv = to_f32(k[at]) * (in_scale ? in_scale[th] : 1.f);
+      la = GR_LOG2E * (per_channel ? log_decay[th * dim + r] : log_decay[th]);
+    }
+    q_s[i * DS + r] = qv;
+    k_s[i * DS + r] = kv;
+    a_s[i * DS + r] = la;
+  }
+  for (int idx = threadIdx.x; idx < GC * GC_COLS; idx += 256) {
+    const int i = idx / GC_COLS, cc = col0 + (idx - i * GC_COLS);
+    float vv = 0.f;
+    if (i < n) {
+      if (cc < vdim) vv = to_f32(v[(size_t)(t0 + i) * in_stride + (size_t)h * vdim + cc]);
+      else if (cc < vcols) vv = 1.f;
+    }
+    v_s[idx] = vv;
+  }
+  __syncthreads();
+  for (int r = threadIdx.x; r < dim; r += 256) {  // A_i: the running sum down the chunk (rows past the last token repeat it)
+    float run = 0.f;
+    for (int i = 0; i < GC; ++i) {
+      run += a_s[i * DS + r];
+      a_s[i * DS + r] = run;
+    }
+  }
+  __syncthreads();
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  float p[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a) p[a][0] = p[a][1] = p[a][2] = p[a][3] = 0.f;
+  // ---- scores inside a sub-chunk: the decay between the two tokens, channel by channel
+  if (tx <= ty) {
+    for (int r = 0; r < dim; ++r) {
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const int i = (ty + 16 * a) * DS + r, j = (tx + 16 * a) * DS + r;
+        p[a][a] += q_s[i] * k_s[j] * gr_exp2(a_s[i] - a_s[j]);
+      }
+    }
+  }
+  __syncthreads();
+  // ---- queries relative to the start of their sub-chunk, keys relative to the end of theirs, and the two inner sub-chunks' decays
+  for (int idx = threadIdx.x; idx < GC * dim; idx += 256) {
+    const int i = idx / dim, r = idx - i * dim;
+    const int sub = i / GC_SUB;
+    const float mine = a_s[i * DS + r];
+    const float before = sub > 0 ? a_s[(sub * GC_SUB - 1) * DS + r] : 0.f;
+    const float end = a_s[(sub * GC_SUB + GC_SUB - 1) * DS + r];
+    q_s[i * DS + r] *= gr_exp2(mine - before);
+    k_s[i * DS + r] *= gr_exp2(end - mine);
+  }
+  for (int idx = threadIdx.x; idx < 2 * dim; idx += 256) {
+    const int w = idx / dim, r = idx - w * dim;  // w = 0: over sub-chunk 1, w = 1: over sub-chunk 2
+    d_s[idx] = gr_exp2(a_s[((w + 2) * GC_SUB - 1) * DS + r] - a_s[((w + 1) * GC_SUB - 1) * DS + r]);
+  }
+  __syncthreads();
+  // ---- scores between sub-chunks
+  for (int r = 0; r < dim; ++r) {
+    const float q1 = q_s[(ty + 16) * DS + r], q2 = q_s[(ty + 32) * DS + r], q3 = q_s[(ty + 48) * DS + r];
+    const float k0 = k_s[tx * DS + r], k1 = k_s[(tx + 16) * DS + r], k2 = k_s[(tx + 32) * DS + r];
+    const float d1 = d_s[r], d2 = d_s[dim + r];
+    p[1][0] += q1 * k0;
+    p[2][1] += q2 * k1;
+    p[3][2] += q3 * k2;
+    p[2][0] += q2 * d1 * k0;
+    p[3][1] += q3 * d2 * k1;
+    p[3][0] += q3 * (d1 * d2) * k0;
+  }
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) p_s[(ty + 16 * a) * (GC + 1) + tx + 16 * b] = p[a][b];  // zero above the diagonal: never added to
+  __syncthreads();
+  // ---- the queries against the state before the chunk take the whole decay since the chunk's start; the state comes through the
+  // keys' place in shared memory, which the scores no longer need
+  for (int idx = threadIdx.x; idx < GC * dim; idx += 256) {
+    const int i = idx / dim, r = idx - i * dim;
+    const int sub = i / GC_SUB;
+    if (sub > 0) q_s[i * DS + r] *= gr_exp2(a_s[(sub * GC_SUB - 1) * DS + r]);
+  }
+  const float* sp = scratch + ((size_t)blockIdx.x * max_chunks + c) * dim * vcols;
+  float* s_s = k_s;  // [dim][GC_COLS]; GC * (dim + 1) >= dim * GC_COLS
+  for (int idx = threadIdx.x; idx < dim * GC_COLS; idx += 256) {
+    const int r = idx / GC_COLS, cc = col0 + (idx - r * GC_COLS);
+    s_s[idx] = cc < vcols ? sp[(size_t)r * vcols + cc] : 0.f;
+  }
+  float acc[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
+  for (int j = 0; j < n; ++j) {
+    const float4 vv = *reinterpret_cast<const float4*>(v_s + j * GC_COLS + 4 * tx);
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const float pv = p_s[(ty + 16 * a) * (GC + 1) + j];
+      acc[a][0] += pv * vv.x;
+      acc[a][1] += pv * vv.y;
+      acc[a][2] += pv * vv.z;
+      acc[a][3] += pv * vv.w;
+    }
+  }
+  __syncthreads();
+  for (int r = 0; r < dim; ++r) {
+    const float4 t = *reinterpret_cast<const float4*>(s_s + r * GC_COLS + 4 * tx);
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const float qv = q_s[(ty + 16 * a) * DS + r];
+      acc[a][0] += qv * t.x;
+      acc[a][1] += qv * t.y;
+      acc[a][2] += qv * t.z;
+      acc[a][3] += qv * t.w;
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const int i = ty + 16 * a;
+    if (i < n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = col0 + 4 * tx + e;
+        if (col < vcols) out[(size_t)(t0 + i) * out_stride + (size_t)h * vcols + col] = acc[a][e];
+      }
+    }
+  }
+}
+
+RL_API long long rl_gated_attn_chunked_scratch_floats(int n_seqs, int max_q_len, int H, int dim, int vcols) {
+  return (long long)n_seqs * H * ((max_q_len + GC - 1) / GC) * dim * (vcols + 1);
+}
+
+static size_t gated_chunk_out_smem(int dim) {
+  return ((size_t)3 * GC * (dim + 1) + GC * GC_COLS + GC * (GC + 1) + 2 * dim) * sizeof(float);
+}
+
+RL_API int rl_gated_attn_chunked_takes(int dim) { return dim > 0 && gated_chunk_out_smem(dim) <= 227 * 1024; }
+
+RL_API int rl_gated_attn_chunked(const void* q, const void* k, const void* v, int dtype, int in_stride, const float* log_decay,
+                                 int per_channel, const float* in_scale, float q_scale, float* state, const int* slot_ids,
+                                 const int* seq_start, float* scratch, float* out, int out_stride, int n_seqs, int max_q_len, int H,
+                                 int dim, int vdim, int ext, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0 || H <= 0 || dim <= 0 || vdim <= 0 || (ext != 0 && ext != 1) || !log_decay || !scratch)
+    RL_REFUSE(1, "gated_attn_chunked: S=%d max_q=%d H=%d dim=%d vdim=%d ext=%d", n_seqs, max_q_len, H, dim, vdim, ext);
+  if (!rl_gated_attn_chunked_takes(dim)) RL_REFUSE(2, "gated_attn_chunked: key size %d needs more shared memory than an SM has", dim);
+  const int vcols = vdim + ext;
+  const int max_chunks = (max_q_len + GC - 1) / GC, col_tiles = (vcols + GC_COLS - 1) / GC_COLS;
+  const long long sh = (long long)n_seqs * H;
+  if (sh > 0x7fffffffLL || max_chunks > 65535 || col_tiles > 65535) RL_REFUSE(3, "gated_attn_chunked: %d chunks or %d column tiles exceed the grid", max_chunks, col_tiles);
+  float* chunk_decay = scratch + sh * max_chunks * dim * vcols;
+  const int elems = dim * vcols;
+  dim3 grid((unsigned)sh, max_chunks, col_tiles), grid2((unsigned)sh, (elems + 255) / 256);
+  const size_t smem1 = ((size_t)GC * dim + GC * GC_COLS) * sizeof(float), smem3 = gated_chunk_out_smem(dim);
+#define RL_GC(T)                                                                                                                     \
+  do {                                                                                                                               \
+    if (cudaFuncSetAttribute(gated_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1) != cudaSuccess || \
+        cudaFuncSetAttribute(gated_chunk_out_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3) != cudaSuccess)     \
+      RL_REFUSE(4, "gated_attn_chunked: %zu bytes of shared memory refused", smem3);                                                 \
+    RL_LAUNCH_CHECK(rl_launch(gated_chunk_state_kernel<T>, grid, 256, smem1, stream, (const T*)k, (const T*)v, in_stride, log_decay,  \
+                              per_channel, in_scale, seq_start, scratch, chunk_decay, max_chunks, H, dim, vdim, ext));               \
+    RL_LAUNCH_CHECK(rl_launch(gated_chunk_scan_kernel, grid2, 256, 0, stream, state, slot_ids, seq_start, scratch,                   \
+                              (const float*)chunk_decay, max_chunks, H, dim, vcols));                                                \
+    RL_LAUNCH_CHECK(rl_launch(gated_chunk_out_kernel<T>, grid, 256, smem3, stream, (const T*)q, (const T*)k, (const T*)v, in_stride,  \
+                              log_decay, per_channel, in_scale, q_scale, seq_start, (const float*)scratch, max_chunks, out,          \
+                              out_stride, H, dim, vdim, ext));                                                                       \
+  } while (0)
+  if (dtype == RL_BF16) RL_GC(bf16);
+  else if (dtype == RL_F32) RL_GC(float);
+  else RL_REFUSE(5, "gated_attn_chunked: unknown dtype %d", dtype);
+#undef RL_GC
+  return 0;
+}
+
 // ---------------------------------------------------------------- per head: normaliser, RMS norm, weight, gate
 // One warp per (token, head).  x: 32-bit rows of H heads of `xh` numbers, of which the first n are the head's values; with m
 // given, x[n] is the head's n . q and the values are first divided by max(|x[n]|, exp(-m)) + den_eps.  Then

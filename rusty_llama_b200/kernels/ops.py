@@ -319,11 +319,13 @@ def attn_decode(
     n_splits: int, scratch: torch.Tensor, window: int = 0, scale: Optional[float] = None,
     out: Optional[torch.Tensor] = None, impl: str = "auto", fuse: int = 0,
     inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, interleaved: bool = False,
-    counters: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
+    counters: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, chunk: int = 0, softcap: float = 0.0,
 ) -> torch.Tensor:
     """One query token per sequence over keys 0..seq_len-1, the key range cut into `n_splits`.
 
     sink: None, or float32 [H]: exp(sink_h) joins the softmax's denominator of head h and nothing else.
+    chunk, softcap (the "tma" kernel only): 0, or the size of the chunks of positions outside of which the query sees nothing,
+    and 0, or the cap c of s <- c tanh(s / c) on the scaled scores.
 
     counters (the "tma" kernel only): int32 zeros, one per sequence and group of 8 query heads of a kv
     head; with them the splits are added up by the block that finishes last instead of by a second
@@ -361,7 +363,8 @@ def attn_decode(
     _need(scratch.numel() >= need, f"attn_decode: scratch holds {scratch.numel()} floats, {need} needed")
     if out is None:
         out = torch.empty((S, num_heads * head_dim), dtype=act, device=q.device)
-    _cuda(out, "attn_decode out", act)
+    _cuda(out, "attn_decode out", act, contiguous=False)
+    _need(_rows(out, "attn_decode out") >= num_heads * head_dim and tuple(out.shape) == (S, num_heads * head_dim), "attn_decode: out must be [S, H head_dim] rows")
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
     n_o = S * num_heads * n_splits * head_dim
@@ -396,10 +399,11 @@ def attn_decode(
             c_int(n_splits), _p(status), c_int(fuse), _p(inv_freq) if (fuse and rotary_dim) else c_void_p(0), c_int(rotary_dim if fuse else 0),
             c_int(1 if interleaved else 0), _p(counters) if counters is not None else c_void_p(0),
             _p(q_parts) if q_parts is not None else c_void_p(0), c_int(0 if q_parts is None else q_parts.shape[0]),
-            c_ll(0 if q_parts is None else q_parts.stride(0)), *_wt(), _p(sink), _stream(),
+            c_ll(0 if q_parts is None else q_parts.stride(0)), *_wt(), _p(sink), c_int(chunk), c_float(softcap), _stream(),
         )
         _check(lib, rc, "attn_decode_tma", kernels=1 if counters is not None else 2)
         return out
+    _need(chunk == 0 and softcap == 0.0, "attn_decode: only the TMA kernel takes chunks and capped scores")
     lib = build.load("attention_decode")
     rc = lib.rl_attn_decode_sink(
         _p(q), c_int(_dt(q, "attn_decode")), c_int(qs), _p(k_pages), _p(v_pages), _p(block_table),
@@ -450,9 +454,11 @@ FLASH_TC_HEAD_DIMS = (64, 128)  # head sizes the tcgen05 prompt attention is bui
 def flash_prefill_tc(
     q: torch.Tensor, k_pages, v_pages, block_table, seq_start, seq_pos0, max_q_len: int, num_heads: int,
     num_kv_heads: int, head_dim: int, window: int = 0, scale: Optional[float] = None,
-    out: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, chunk: int = 0, softcap: float = 0.0,
 ) -> torch.Tensor:
-    """`flash_prefill` on the tcgen05 tensor cores (TMA-fed, S and P V in tensor memory); head sizes 64 and 128."""
+    """`flash_prefill` on the tcgen05 tensor cores (TMA-fed, S and P V in tensor memory); head sizes 64 and 128.
+    chunk: 0, or the size of the chunks of positions (counted from 0) outside of which a query sees nothing; softcap: 0, or the
+    cap c of s <- c tanh(s / c) on the scaled scores."""
     _need(head_dim in FLASH_TC_HEAD_DIMS, f"flash_prefill_tc: head size {head_dim}, this kernel is built for {FLASH_TC_HEAD_DIMS}")
     _cuda(q, "flash_prefill_tc q", torch.bfloat16, contiguous=False)
     qs = _rows(q, "flash_prefill_tc q")
@@ -467,7 +473,8 @@ def flash_prefill_tc(
     _need(seq_start.numel() == S + 1 and block_table.dim() == 2 and block_table.shape[0] >= S, "flash_prefill_tc: metadata sizes")
     if out is None:
         out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=q.device)
-    _cuda(out, "flash_prefill_tc out", torch.bfloat16)
+    _cuda(out, "flash_prefill_tc out", torch.bfloat16, contiguous=False)
+    _need(_rows(out, "flash_prefill_tc out") % 8 == 0 and tuple(out.shape) == (T, num_heads * head_dim), "flash_prefill_tc: out must be [T, H head_dim] rows at 16-byte steps")
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
     _check_sink(sink, num_heads, "flash_prefill_tc")
@@ -476,7 +483,8 @@ def flash_prefill_tc(
     rc = lib.rl_flash_prefill_tc(
         _p(q), c_int(qs), c_int(T), _p(k_pages), _p(v_pages), c_int(k_pages.shape[0]), _p(block_table),
         c_int(block_table.shape[1]), _p(seq_start), _p(seq_pos0), _p(out), c_int(out.stride(0)), c_int(S), c_int(max_q_len),
-        c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _p(status), *_wt(), _p(sink), _stream(),
+        c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _p(status), *_wt(), _p(sink),
+        c_int(chunk), c_float(softcap), _stream(),
     )
     _check(lib, rc, "flash_prefill_tc")
     return out
@@ -1564,9 +1572,55 @@ def gated_attn(
     return out
 
 
+GATED_CHUNK = 64  # tokens per chunk of the chunked recurrence
+
+
 def gated_attn_chunked_takes(dim: int, vcols: int) -> bool:
-    """Whether the chunked form of `gated_attn` is built for these sizes."""
-    return False
+    """Whether the chunked form of `gated_attn` is built for these sizes (its last kernel keeps three [64, dim + 1] tiles in shared memory)."""
+    return dim > 0 and (3 * GATED_CHUNK * (dim + 1) + GATED_CHUNK * 64 + GATED_CHUNK * (GATED_CHUNK + 1) + 2 * dim) * 4 <= 227 * 1024
+
+
+def gated_attn_chunked_scratch_floats(n_seqs: int, max_q_len: int, num_heads: int, dim: int, vcols: int) -> int:
+    """Floats of scratch that `gated_attn_chunked` needs: a [dim, vcols] matrix and a row of dim decays per (sequence, head, chunk)."""
+    return n_seqs * num_heads * ((max_q_len + GATED_CHUNK - 1) // GATED_CHUNK) * dim * (vcols + 1)
+
+
+def gated_attn_chunked(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay: torch.Tensor, in_scale: Optional[torch.Tensor], state: torch.Tensor,
+    slot_ids: torch.Tensor, seq_start: torch.Tensor, num_heads: int, dim: int, vdim: int, max_q_len: int, scratch: torch.Tensor,
+    q_scale: float = 1.0, ext: bool = False,
+) -> torch.Tensor:
+    """`gated_attn` chunk by chunk (64 tokens, all chunks side by side, 32-bit arithmetic): equal within rounding, for prompts.
+    max_q_len: the most tokens a sequence of the step brings; scratch: float32, at least `gated_attn_chunked_scratch_floats(...)`."""
+    for name, t, n in (("q", q, num_heads * dim), ("k", k, num_heads * dim), ("v", v, num_heads * vdim)):
+        _cuda(t, f"gated_attn_chunked {name}", q.dtype, contiguous=False)
+        _need(_rows(t, f"gated_attn_chunked {name}") == q.stride(0) and t.shape[1] == n and t.shape[0] == q.shape[0], f"gated_attn_chunked: {name} has the wrong shape or stride")
+    T = q.shape[0]
+    vcols = vdim + (1 if ext else 0)
+    _need(gated_attn_chunked_takes(dim, vcols), f"gated_attn_chunked: key size {dim} is too large for the chunked kernels")
+    _cuda(log_decay, "gated_attn_chunked log_decay", torch.float32)
+    per_channel = log_decay.numel() == T * num_heads * dim
+    _need(per_channel or log_decay.numel() == T * num_heads, f"gated_attn_chunked: log_decay {tuple(log_decay.shape)} is neither [T, H dim] nor [T, H]")
+    if in_scale is not None:
+        _cuda(in_scale, "gated_attn_chunked in_scale", torch.float32)
+        _need(in_scale.numel() == T * num_heads, "gated_attn_chunked: in_scale must be [T, H]")
+    _cuda(state, "gated_attn_chunked state", torch.float32)
+    _need(state.dim() == 4 and tuple(state.shape[1:]) == (num_heads, dim, vcols), f"gated_attn_chunked: state {tuple(state.shape)} is not [slots, {num_heads}, {dim}, {vcols}]")
+    _cuda(slot_ids, "gated_attn_chunked slot_ids", torch.int32)
+    _cuda(seq_start, "gated_attn_chunked seq_start", torch.int32)
+    S = slot_ids.numel()
+    _need(seq_start.numel() == S + 1, "gated_attn_chunked: seq_start must hold one more entry than there are sequences")
+    _cuda(scratch, "gated_attn_chunked scratch", torch.float32)
+    _need(max_q_len >= 1 and scratch.numel() >= gated_attn_chunked_scratch_floats(S, max_q_len, num_heads, dim, vcols), "gated_attn_chunked: scratch too small")
+    out = torch.empty((T, num_heads * vcols), dtype=torch.float32, device=q.device)
+    lib = build.load("gated_recurrent")
+    rc = lib.rl_gated_attn_chunked(
+        _p(q), _p(k), _p(v), c_int(_dt(q, "gated_attn_chunked")), c_int(q.stride(0)), _p(log_decay), c_int(1 if per_channel else 0), _p(in_scale),
+        c_float(q_scale), _p(state), _p(slot_ids), _p(seq_start), _p(scratch), _p(out), c_int(out.stride(0)), c_int(S), c_int(max_q_len),
+        c_int(num_heads), c_int(dim), c_int(vdim), c_int(1 if ext else 0), _stream(),
+    )
+    _check(lib, rc, "gated_attn_chunked", kernels=3)
+    return out
 
 
 GATE_NONE, GATE_SIGMOID, GATE_SILU = 0, 1, 2
@@ -1660,10 +1714,11 @@ def fold_queries(q: torch.Tensor, mix: torch.Tensor, num_heads: int, num_kv_head
 def flash_mix(
     q: torch.Tensor, k_pages, v_pages, block_table, seq_start, seq_pos0, max_q_len: int, num_heads: int, num_kv_heads: int, kdim: int,
     vdim: int, scale: float, window: int = 0, sink: Optional[torch.Tensor] = None, folded: bool = False, gate: Optional[torch.Tensor] = None,
-    out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
+    out_scale: float = 1.0, out: Optional[torch.Tensor] = None, chunk: int = 0, softcap: float = 0.0,
 ) -> torch.Tensor:
     """bfloat16 attention of a ragged batch over the paged cache on the tensor cores, keys of `kdim` and values of `vdim` numbers,
-    with a window, a sink, a gate (out *= sigmoid(gate)) and a constant factor.  folded: q is what `fold_queries` made
+    with a window, chunks (a query sees the keys of its own chunk of positions only), capped scores (s <- c tanh(s / c)), a sink,
+    a gate (out *= sigmoid(gate)) and a constant factor.  folded: q is what `fold_queries` made
     ([T, H K kdim]: the heads' scores are mixed); else q holds [T, >= H kdim] rows."""
     _cuda(q, "flash_mix q", torch.bfloat16, contiguous=False)
     qs = _rows(q, "flash_mix q")
@@ -1692,7 +1747,7 @@ def flash_mix(
         _p(q), c_ll(qs), c_int(parts * kdim), c_int(parts), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]),
         _p(seq_start), _p(seq_pos0), _p(sink), _p(gate), c_int(gs), c_float(out_scale), _p(out), c_int(out.stride(0)), c_int(S),
         c_int(max_q_len), c_int(num_heads), c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(PAGE_SIZE), c_int(window), c_float(scale),
-        _stream(),
+        c_int(chunk), c_float(softcap), _stream(),
     )
     _check(lib, rc, "flash_mix")
     return out
@@ -1716,7 +1771,7 @@ def flash_mix_decode_scratch_floats(n_seqs: int, num_heads: int, vdim: int, n_sp
 def flash_mix_decode(
     qf: torch.Tensor, k_pages, v_pages, block_table, seq_pos0, num_heads: int, num_kv_heads: int, kdim: int, vdim: int, scale: float,
     n_splits: int, scratch: torch.Tensor, window: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-    out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
+    out_scale: float = 1.0, out: Optional[torch.Tensor] = None, chunk: int = 0, softcap: float = 0.0,
 ) -> torch.Tensor:
     """One query token per sequence, at position seq_pos0[s], over its sequence's cached keys (its own among them), the key range
     cut into `n_splits` parts; a block's rows are the heads.  qf: folded queries [S, H K kdim] (`fold_queries`, with the identity
@@ -1748,7 +1803,7 @@ def flash_mix_decode(
         _p(qf), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]), _p(seq_pos0), _p(sink), _p(gate), c_int(gs),
         c_float(out_scale), c_void_p(scratch.data_ptr()), c_void_p(scratch.data_ptr() + 4 * n_o), _p(out), c_int(out.stride(0)), c_int(S),
         c_int(num_heads), c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(PAGE_SIZE), c_int(window), c_float(scale), c_int(n_splits),
-        _stream(),
+        c_int(chunk), c_float(softcap), _stream(),
     )
     _check(lib, rc, "flash_mix_decode", kernels=2)
     return out

@@ -204,39 +204,69 @@ class Attention(Mixer):
             norm_eps=self.qk_norm_eps or 0.0,
         )
         gate = proj[:, self.qd + self.kvd + self.vvd :] if self.has_gate else None
+        return self._attend(proj, gate, step, cache, out), self.w_o
+
+    def _attend(self, proj: torch.Tensor, gate, step, cache, out):
+        """The attention itself over rows whose queries are ready and whose keys and values are in the cache.  bfloat16 runs take
+        the tcgen05 prompt kernel and the TMA-fed decode kernel where the sizes are theirs (equal key and value sizes of 64 or
+        128, no mixed scores, no gate), else the tensor-core kernel for unequal sizes, mixed scores and gates; 32-bit runs and
+        the remaining sizes take the general kernel."""
+        bf = self.rt.dtype == torch.bfloat16
+        if (bf and self.hd == self.vd and self.hd in ops.FLASH_TC_HEAD_DIMS and not self.has_mix and gate is None and self.out_scale == 1.0
+                and proj.stride(0) % 8 == 0 and proj.data_ptr() % 16 == 0):
+            direct = out is not None and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and out.stride(1) == 1
+            if step.decode_only and self.hd in ops.ATTN_DECODE_TMA_HEAD_DIMS:
+                keys = min(self.window, step.plan_kv_len) if self.window else step.plan_kv_len
+                keys = min(self.chunk, keys) if self.chunk else keys
+                n_splits = decode_splits(step.n_seqs, self.H, self.K, keys, self.hd)
+                scratch = self.rt.workspace.get("attn_decode", ops.attn_decode_scratch_floats(step.n_seqs, self.H, self.hd, n_splits), torch.float32)
+                a = ops.attn_decode(
+                    proj, cache.k_pages, cache.v_pages, cache.block_table, step.seq_len, self.H, self.K, self.hd, n_splits, scratch,
+                    window=self.window, scale=self.scale, sink=self.sink, chunk=self.chunk, softcap=self.softcap, impl="tma",
+                    out=out if direct else None,
+                )
+            else:
+                a = ops.flash_prefill_tc(
+                    proj, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0, step.max_q_len, self.H, self.K,
+                    self.hd, window=self.window, scale=self.scale, sink=self.sink, chunk=self.chunk, softcap=self.softcap,
+                    out=out if direct else None,
+                )
+            if out is not None and a is not out:
+                out.copy_(a)
+                a = out
+            return a
         parts = self.K if self.has_mix else 1
-        if (self.rt.dtype == torch.bfloat16 and ops.flash_mix_takes(self.hd, self.vd, parts) and proj.stride(0) % 8 == 0 and not self.softcap and not self.chunk
+        if (bf and ops.flash_mix_takes(self.hd, self.vd, parts) and proj.stride(0) % 8 == 0
                 and (out is None or (out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)) and (self.qd + self.kvd + self.vvd) % 2 == 0):
             if step.decode_only and ops.flash_mix_decode_takes(self.H, self.K, self.hd, self.vd):
                 # single tokens: all heads of a sequence are the rows of one block, which reads a key tile once for all of them;
                 # the key range is cut into parts of a page or more so that the blocks fill the GPU (a block is one or two warps: short chains matter more than few parts)
                 if self.fold_matrix is None:
-                    self.fold_matrix = self.mix if self.has_mix else torch.eye(self.H, dtype=torch.float32, device=xn.device)
+                    self.fold_matrix = self.mix if self.has_mix else torch.eye(self.H, dtype=torch.float32, device=proj.device)
                 qf = ops.fold_queries(proj, self.fold_matrix, self.H, self.K, self.hd)
                 keys = min(self.window, step.plan_kv_len) if self.window else step.plan_kv_len
+                keys = min(self.chunk, keys) if self.chunk else keys
                 pages = (keys + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE + 1
-                n_splits = max(1, min(2 * sm_count(xn.device) // step.n_seqs, pages, 64))
+                n_splits = max(1, min(2 * sm_count(proj.device) // step.n_seqs, pages, 64))
                 scratch = self.rt.workspace.get("flash_mix_decode", ops.flash_mix_decode_scratch_floats(step.n_seqs, self.H, self.vd, n_splits), torch.float32)
-                a = ops.flash_mix_decode(
+                return ops.flash_mix_decode(
                     qf, cache.k_pages, cache.v_pages, cache.block_table, step.seq_pos0, self.H, self.K, self.hd, self.vd, self.scale,
-                    n_splits, scratch, window=self.window, sink=self.sink, gate=gate, out_scale=self.out_scale, out=out,
+                    n_splits, scratch, window=self.window, sink=self.sink, gate=gate, out_scale=self.out_scale, out=out, chunk=self.chunk,
+                    softcap=self.softcap,
                 )
-                return a, self.w_o
             # the tensor-core kernel for prompts (and single tokens of sizes the decode kernel does not take); mixed scores come
             # from folded queries
             q = ops.fold_queries(proj, self.mix, self.H, self.K, self.hd) if self.has_mix else proj
-            a = ops.flash_mix(
+            return ops.flash_mix(
                 q, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0, step.max_q_len, self.H, self.K,
                 self.hd, self.vd, self.scale, window=self.window, sink=self.sink, folded=self.has_mix, gate=gate, out_scale=self.out_scale,
-                out=out,
+                out=out, chunk=self.chunk, softcap=self.softcap,
             )
-            return a, self.w_o
-        a = ops.attn_ext(
+        return ops.attn_ext(
             proj, cache.k_pages, cache.v_pages, cache.block_table, step.tok_seq, step.tok_pos, self.H, self.K, self.hd, self.vd,
             self.scale, window=self.window, sink=self.sink, mix=self.mix, gate=gate, out_scale=self.out_scale, out=out, chunk=self.chunk,
             softcap=self.softcap,
         )
-        return a, self.w_o
 
     def forward_unprojected(self, xn: torch.Tensor, step, cache, shared_cache: bool = False, out=None):
         """out: None, or a [T, H value_dim] view (dense rows, any row stride) that receives the heads' result."""
@@ -295,3 +325,32 @@ class Attention(Mixer):
                 step.max_q_len, self.H, self.K, self.hd, window=self.window, scale=self.scale, sink=self.sink,
             )
         return a, self.w_o
+
+
+def chunked_attention_runner(proj, k_pages, v_pages, block_table, step, num_heads: int, num_kv_heads: int, kdim: int, vdim: int, scale: float,
+                             chunk: int, softcap: float, sink, window: int = 0, workspace=None):
+    """A callable that runs the attention of `Attention` (the kernel choice included) over ready rows, for timing it alone.
+    step: tok_seq, tok_pos, seq_start, seq_pos0, seq_len (or none: positions after the step), max_q_len, n_seqs, decode_only."""
+    from types import SimpleNamespace
+
+    class _Scratch:
+        def __init__(self):
+            self.held = {}
+
+        def get(self, name, numel, dtype, zeroed=False):
+            buf = self.held.get(name)
+            if buf is None or buf.numel() < numel or buf.dtype != dtype:
+                buf = self.held[name] = torch.zeros(int(numel), dtype=dtype, device=proj.device)
+            return buf
+
+    if not hasattr(step, "seq_len"):
+        step.seq_len = (step.seq_pos0 + (step.seq_start[1:] - step.seq_start[:-1])).to(torch.int32)
+    if not hasattr(step, "plan_kv_len"):
+        step.plan_kv_len = int(step.seq_len.max())
+    part = SimpleNamespace(
+        rt=SimpleNamespace(dtype=proj.dtype, workspace=workspace or _Scratch()), H=num_heads, K=num_kv_heads, hd=kdim, vd=vdim, scale=scale,
+        window=window, chunk=chunk, softcap=softcap, sink=sink, mix=None, has_mix=False, out_scale=1.0, fold_matrix=None,
+        qd=num_heads * kdim, kvd=num_kv_heads * kdim, vvd=num_kv_heads * vdim,
+    )
+    cache = SimpleNamespace(k_pages=k_pages, v_pages=v_pages, block_table=block_table)
+    return lambda: Attention._attend(part, proj, None, step, cache, None)
