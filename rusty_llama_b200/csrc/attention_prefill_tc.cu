@@ -415,7 +415,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       // few warps of an SM waiting on their own arithmetic)
       if (softcap != 0.f) {
 #pragma unroll
-        for (int i = 0; i < BNK; ++i) v[i] = __float_as_uint(tanhf(__uint_as_float(v[i]) * cap_in));
+        for (int i = 0; i < BNK; ++i) v[i] = __float_as_uint(rl_tanh_sfu(__uint_as_float(v[i]) * cap_in));
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {

@@ -137,12 +137,21 @@ __device__ __forceinline__ int rl_first_key(int pos, int window, int chunk) {
   return first;
 }
 
+// tanh for the capped scores of the bfloat16 attention kernels: 1 - 2 / (exp(2x) + 1) on the special-function unit (two of its
+// operations and three others, where tanhf takes a branch and a polynomial).  The absolute error stays near 2e-7 for every x
+// (which is what a score's exponential sees); the relative error of small results does not.
+__device__ __forceinline__ float rl_tanh_sfu(float x) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(fminf(x, 15.f) * 2.885390081777927f));  // tanh(15) rounds to 1; no infinity reaches the division
+  return 1.f - __fdividef(2.f, e + 1.f);
+}
+
 // A raw score q . k as an exponent of two: raw * scale_log2 (scale_log2 = scale * log2 e), or with a cap c on the scaled
 // score, c tanh(raw * scale / c) * log2 e.
 __device__ __forceinline__ float rl_score_log2(float raw, float scale_log2, float softcap) {
   if (softcap == 0.f) return raw * scale_log2;
   const float cap_log2 = softcap * 1.4426950408889634f;
-  return cap_log2 * tanhf(raw * (scale_log2 / cap_log2));
+  return cap_log2 * rl_tanh_sfu(raw * (scale_log2 / cap_log2));
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -100,10 +100,82 @@ __global__ void mlstm_gates_kernel(const T* __restrict__ gi, const T* __restrict
   if (lane == 0) *mp = m;
 }
 
+// The same for long prompts: a block of MG_WARPS warps per (sequence, head) takes 32 MG_WARPS tokens at a time.  A token is the map
+// m -> max(m + f, i); two maps in a row are again such a map, (f1, i1) then (f2, i2) = (f1 + f2, max(i1 + f2, i2)), so a warp
+// composes its 32 maps by a scan of five shuffles, the warps' totals go through shared memory, and every token applies its
+// composed map to the maximum that entered the round.  The sums of f are taken in another order than token by token: equal
+// within rounding, not in bits, and the order depends on where the step starts.
+#define MG_WARPS 8
+
+template <typename T>
+__global__ void __launch_bounds__(32 * MG_WARPS)
+mlstm_gates_scan_kernel(const T* __restrict__ gi, const T* __restrict__ gf, int in_stride, const float* __restrict__ bias_i,
+                        const float* __restrict__ bias_f, float cap, float* __restrict__ m_state, const int* __restrict__ slot_ids,
+                        const int* __restrict__ seq_start, float* __restrict__ log_a, float* __restrict__ b_out,
+                        float* __restrict__ m_out, int H) {
+  __shared__ float tot_f[MG_WARPS], tot_i[MG_WARPS];
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int s = blockIdx.x / H, h = blockIdx.x % H;
+  const int t0 = seq_start[s], t1 = seq_start[s + 1];
+  float* mp = m_state + (size_t)slot_ids[s] * H + h;
+  float m_in = *mp;
+  const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
+  const float inv_cap = 1.0f / cap;
+  for (int base = t0; base < t1; base += 32 * MG_WARPS) {
+    const int t = base + threadIdx.x;
+    float li = -INFINITY, lf = 0.f;  // past the end: the map that changes nothing
+    if (t < t1) {
+      li = cap * tanhf((to_f32(gi[(size_t)t * in_stride + h]) + bi) * inv_cap);
+      lf = gr_log_logistic(cap * tanhf((to_f32(gf[(size_t)t * in_stride + h]) + bf) * inv_cap));
+    }
+    float F = lf, I = li;  // the tokens of this warp up to and with this lane's, as one map
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float Fp = __shfl_up_sync(0xffffffffu, F, o), Ip = __shfl_up_sync(0xffffffffu, I, o);
+      if (lane >= o) {
+        I = fmaxf(Ip + F, I);
+        F = Fp + F;
+      }
+    }
+    if (lane == 31) {
+      tot_f[warp] = F;
+      tot_i[warp] = I;
+    }
+    __syncthreads();
+    float m_w = m_in;  // the maximum that enters this warp's tokens
+    for (int w = 0; w < warp; ++w) m_w = fmaxf(m_w + tot_f[w], tot_i[w]);
+    const float m_new = fmaxf(m_w + F, I);
+    float m_prev = __shfl_up_sync(0xffffffffu, m_new, 1);
+    if (lane == 0) m_prev = m_w;
+    if (t < t1) {
+      log_a[(size_t)t * H + h] = lf + m_prev - m_new;
+      b_out[(size_t)t * H + h] = expf(li - m_new);
+      m_out[(size_t)t * H + h] = m_new;
+    }
+    for (int w = warp; w < MG_WARPS; ++w) m_w = fmaxf(m_w + tot_f[w], tot_i[w]);  // the maximum after the round, in every thread
+    m_in = m_w;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *mp = m_in;
+}
+
 RL_API int rl_mlstm_gates(const void* gi, const void* gf, int dtype, int in_stride, const float* bias_i, const float* bias_f, float cap,
                           float* m_state, const int* slot_ids, const int* seq_start, float* log_a, float* b_out, float* m_out,
-                          int n_seqs, int H, cudaStream_t stream) {
+                          int n_seqs, int H, int scan, cudaStream_t stream) {
   if (n_seqs <= 0 || H <= 0 || !(cap > 0.f)) RL_REFUSE(1, "mlstm_gates: S=%d H=%d cap=%g", n_seqs, H, (double)cap);
+  if (scan) {
+    if (dtype == RL_BF16)
+      RL_LAUNCH_CHECK(rl_launch(mlstm_gates_scan_kernel<bf16>, n_seqs * H, 32 * MG_WARPS, 0, stream, (const bf16*)gi, (const bf16*)gf, in_stride,
+                                bias_i, bias_f, cap, m_state, slot_ids, seq_start, log_a, b_out, m_out, H));
+    else if (dtype == RL_F32)
+      RL_LAUNCH_CHECK(rl_launch(mlstm_gates_scan_kernel<float>, n_seqs * H, 32 * MG_WARPS, 0, stream, (const float*)gi, (const float*)gf,
+                                in_stride, bias_i, bias_f, cap, m_state, slot_ids, seq_start, log_a, b_out, m_out, H));
+    else
+      RL_REFUSE(2, "mlstm_gates: unknown dtype %d", dtype);
+    return 0;
+  }
   if (dtype == RL_BF16)
     RL_LAUNCH_CHECK(rl_launch(mlstm_gates_kernel<bf16>, n_seqs * H, 32, 0, stream, (const bf16*)gi, (const bf16*)gf, in_stride, bias_i, bias_f,
                               cap, m_state, slot_ids, seq_start, log_a, b_out, m_out, H));

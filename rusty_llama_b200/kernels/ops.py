@@ -1505,11 +1505,13 @@ def gla_log_decay(z: torch.Tensor, bias: Optional[torch.Tensor], tau: float) -> 
 
 def mlstm_gates(
     gi: torch.Tensor, gf: torch.Tensor, bias_i: Optional[torch.Tensor], bias_f: Optional[torch.Tensor], cap: float, m_state: torch.Tensor,
-    slot_ids: torch.Tensor, seq_start: torch.Tensor,
+    slot_ids: torch.Tensor, seq_start: torch.Tensor, scan: bool = False,
 ):
     """The gates of a matrix memory.  gi, gf: [T, H] views of one projection's rows (the raw input and forget gates); biases float32 [H].
     With i = cap tanh((gi + b_i) / cap), f = logsigmoid(cap tanh((gf + b_f) / cap)) and the running maximum m_t = max(f_t + m_(t-1), i_t)
-    carried in m_state float32 [slots, H]: returns (log_a = f + m_(t-1) - m_t, b = exp(i - m_t), m), each float32 [T, H]."""
+    carried in m_state float32 [slots, H]: returns (log_a = f + m_(t-1) - m_t, b = exp(i - m_t), m), each float32 [T, H].
+    scan: 256 tokens of a sequence at a time, their maps m -> max(m + f, i) composed by a scan (long prompts; equal within rounding);
+    else token after token (equal bits however a sequence is cut into steps)."""
     _cuda(gi, "mlstm_gates gi", contiguous=False)
     _cuda(gf, "mlstm_gates gf", gi.dtype, contiguous=False)
     stride = _rows(gi, "mlstm_gates gi")
@@ -1529,7 +1531,7 @@ def mlstm_gates(
     lib = build.load("gated_recurrent")
     rc = lib.rl_mlstm_gates(
         _p(gi), _p(gf), c_int(_dt(gi, "mlstm_gates")), c_int(stride), _p(bias_i), _p(bias_f), c_float(cap), _p(m_state), _p(slot_ids),
-        _p(seq_start), _p(log_a), _p(b), _p(m), c_int(S), c_int(H), _stream(),
+        _p(seq_start), _p(log_a), _p(b), _p(m), c_int(S), c_int(H), c_int(1 if scan else 0), _stream(),
     )
     _check(lib, rc, "mlstm_gates")
     return log_a, b, m

@@ -119,7 +119,7 @@ def kernel_table(z: dict, T: int, batch: int, ctx: int, peaks: dict) -> Dict[str
                 m_state = torch.zeros(n_seqs, heads, device=dev)
                 bz = torch.zeros(heads, device=dev)
                 gi, gf = proj[:, 4 * qd: 4 * qd + heads], proj[:, 4 * qd + heads:]
-                us = mb._time(lambda i: ops.mlstm_gates(gi, gf, bz, bz, 15.0, m_state, step.slot_ids, step.seq_start), 1, **it)
+                us = mb._time(lambda i: ops.mlstm_gates(gi, gf, bz, bz, 15.0, m_state, step.slot_ids, step.seq_start, scan=prompt), 1, **it)
                 note(f"{tag}_mlstm_gates", us, rows * heads * (4 + 12), 0)
                 log_a, b, m = ops.mlstm_gates(gi, gf, bz, bz, 15.0, m_state, step.slot_ids, step.seq_start)
             else:

@@ -210,7 +210,8 @@ class MatrixMemory(Mixer):
         q, k, v = proj[:, :qd], proj[:, qd : 2 * qd], proj[:, 2 * qd : 2 * qd + vd]
         gate = proj[:, 2 * qd + vd : 2 * qd + 2 * vd]
         gi, gf = proj[:, 2 * qd + 2 * vd : 2 * qd + 2 * vd + H], proj[:, 2 * qd + 2 * vd + H :]
-        log_a, b, m = ops.mlstm_gates(gi, gf, self.b_i, self.b_f, self.cap, maximum.state, step.slot_ids, step.seq_start)
+        log_a, b, m = ops.mlstm_gates(gi, gf, self.b_i, self.b_f, self.cap, maximum.state, step.slot_ids, step.seq_start,
+                                      scan=xn.dtype == torch.bfloat16 and step.max_q_len >= _CHUNKED_MIN_TOKENS)
         o = _recurrence(self, q, k, v, log_a, b, memory.state, step, ext=True)
         a = ops.head_norm_gate(
             o, H, self.vdim, self.w_norm, self.eps, gate, ops.GATE_SIGMOID, xn.dtype, m=m, den_eps=self.den_eps, out_scale=self.out_scale, out=out,
