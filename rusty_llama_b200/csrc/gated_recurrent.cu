@@ -439,8 +439,10 @@ __global__ void gated_chunk_scan_kernel(float* __restrict__ state, const int* __
   *st = S;
 }
 
-// (3): grid as (1).  Thread (ty, tx): scores P[ty + 16 a][tx + 16 b] (a, b: the sub-chunks of the query and of the key), then
-// outputs for rows ty + 16 a and columns 4 tx .. 4 tx + 3.
+// (3): grid (S * H, chunks).  Thread (ty, tx): scores P[ty + 16 a][tx + 16 b] (a, b: the sub-chunks of the query and of the key),
+// computed once; then, column tile after column tile, outputs for rows ty + 16 a and columns 4 tx .. 4 tx + 3.  The scores and the
+// values' tile take the place of the decays' sums, and the state's tile the keys' place, once those are used up: three tiles of
+// [GC][dim + 1] in all, so that two blocks share an SM at dim = 128.
 template <typename T>
 __global__ void __launch_bounds__(256)
 gated_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int in_stride,
@@ -450,18 +452,18 @@ gated_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
   extern __shared__ float sm[];
   pdl_trigger();
   pdl_wait();
-  const int s = blockIdx.x / H, h = blockIdx.x % H, c = blockIdx.y, col0 = blockIdx.z * GC_COLS;
+  const int s = blockIdx.x / H, h = blockIdx.x % H, c = blockIdx.y;
   const int vcols = vdim + ext;
   const int t0 = seq_start[s] + c * GC;
   const int n = min(GC, seq_start[s + 1] - t0);
   if (n <= 0) return;
   const int DS = dim + 1;  // rows one apart in the banks
   float* q_s = sm;                    // [GC][DS]
-  float* k_s = q_s + GC * DS;         // [GC][DS]
-  float* a_s = k_s + GC * DS;         // [GC][DS]: A_i in units of log 2
-  float* v_s = a_s + GC * DS;         // [GC][GC_COLS]
+  float* k_s = q_s + GC * DS;         // [GC][DS]; later the state's tile [dim][GC_COLS]
+  float* a_s = k_s + GC * DS;         // [GC][DS]: A_i in units of log 2; later v_s and p_s
+  float* v_s = a_s;                   // [GC][GC_COLS]
   float* p_s = v_s + GC * GC_COLS;    // [GC][GC + 1]
-  float* d_s = p_s + GC * (GC + 1);   // [2][dim]: the decay over sub-chunk 1 and over sub-chunk 2
+  float* d_s = a_s + max(GC * DS, GC * GC_COLS + GC * (GC + 1));  // [5][dim]: the decay over sub-chunk 1 and over sub-chunk 2; A at the ends of sub-chunks 0, 1, 2
   for (int idx = threadIdx.x; idx < GC * dim; idx += 256) {
     const int i = idx / dim, r = idx - i * dim;
     float qv = 0.f, kv = 0.f, la = 0.f;
@@ -475,15 +477,6 @@ gated_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
     q_s[i * DS + r] = qv;
     k_s[i * DS + r] = kv;
     a_s[i * DS + r] = la;
-  }
-  for (int idx = threadIdx.x; idx < GC * GC_COLS; idx += 256) {
-    const int i = idx / GC_COLS, cc = col0 + (idx - i * GC_COLS);
-    float vv = 0.f;
-    if (i < n) {
-      if (cc < vdim) vv = to_f32(v[(size_t)(t0 + i) * in_stride + (size_t)h * vdim + cc]);
-      else if (cc < vcols) vv = 1.f;
-    }
-    v_s[idx] = vv;
   }
   __syncthreads();
   for (int r = threadIdx.x; r < dim; r += 256) {  // A_i: the running sum down the chunk (rows past the last token repeat it)
@@ -523,7 +516,11 @@ gated_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
     const int w = idx / dim, r = idx - w * dim;  // w = 0: over sub-chunk 1, w = 1: over sub-chunk 2
     d_s[idx] = gr_exp2(a_s[((w + 2) * GC_SUB - 1) * DS + r] - a_s[((w + 1) * GC_SUB - 1) * DS + r]);
   }
-  __syncthreads();
+  for (int idx = threadIdx.x; idx < 3 * dim; idx += 256) {
+    const int w = idx / dim, r = idx - w * dim;
+    d_s[2 * dim + idx] = a_s[((w + 1) * GC_SUB - 1) * DS + r];
+  }
+  __syncthreads();  // the decays' sums are used up from here on
   // ---- scores between sub-chunks
   for (int r = 0; r < dim; ++r) {
     const float q1 = q_s[(ty + 16) * DS + r], q2 = q_s[(ty + 32) * DS + r], q3 = q_s[(ty + 48) * DS + r];
@@ -541,53 +538,64 @@ gated_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
 #pragma unroll
     for (int b = 0; b < 4; ++b) p_s[(ty + 16 * a) * (GC + 1) + tx + 16 * b] = p[a][b];  // zero above the diagonal: never added to
   __syncthreads();
-  // ---- the queries against the state before the chunk take the whole decay since the chunk's start; the state comes through the
-  // keys' place in shared memory, which the scores no longer need
+  // ---- the queries against the state before the chunk take the whole decay since the chunk's start
   for (int idx = threadIdx.x; idx < GC * dim; idx += 256) {
     const int i = idx / dim, r = idx - i * dim;
     const int sub = i / GC_SUB;
-    if (sub > 0) q_s[i * DS + r] *= gr_exp2(a_s[(sub * GC_SUB - 1) * DS + r]);
+    if (sub > 0) q_s[i * DS + r] *= gr_exp2(d_s[(sub + 1) * dim + r]);
   }
   const float* sp = scratch + ((size_t)blockIdx.x * max_chunks + c) * dim * vcols;
   float* s_s = k_s;  // [dim][GC_COLS]; GC * (dim + 1) >= dim * GC_COLS
-  for (int idx = threadIdx.x; idx < dim * GC_COLS; idx += 256) {
-    const int r = idx / GC_COLS, cc = col0 + (idx - r * GC_COLS);
-    s_s[idx] = cc < vcols ? sp[(size_t)r * vcols + cc] : 0.f;
-  }
-  float acc[4][4];
+  for (int col0 = 0; col0 < vcols; col0 += GC_COLS) {
+    __syncthreads();  // scores and queries written, keys read (first tile); the tile before read
+    for (int idx = threadIdx.x; idx < GC * GC_COLS; idx += 256) {
+      const int i = idx / GC_COLS, cc = col0 + (idx - i * GC_COLS);
+      float vv = 0.f;
+      if (i < n) {
+        if (cc < vdim) vv = to_f32(v[(size_t)(t0 + i) * in_stride + (size_t)h * vdim + cc]);
+        else if (cc < vcols) vv = 1.f;
+      }
+      v_s[idx] = vv;
+    }
+    for (int idx = threadIdx.x; idx < dim * GC_COLS; idx += 256) {
+      const int r = idx / GC_COLS, cc = col0 + (idx - r * GC_COLS);
+      s_s[idx] = cc < vcols ? sp[(size_t)r * vcols + cc] : 0.f;
+    }
+    __syncthreads();
+    float acc[4][4];
 #pragma unroll
-  for (int a = 0; a < 4; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
-  for (int j = 0; j < n; ++j) {
-    const float4 vv = *reinterpret_cast<const float4*>(v_s + j * GC_COLS + 4 * tx);
+    for (int a = 0; a < 4; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
+    for (int j = 0; j < n; ++j) {
+      const float4 vv = *reinterpret_cast<const float4*>(v_s + j * GC_COLS + 4 * tx);
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const float pv = p_s[(ty + 16 * a) * (GC + 1) + j];
+        acc[a][0] += pv * vv.x;
+        acc[a][1] += pv * vv.y;
+        acc[a][2] += pv * vv.z;
+        acc[a][3] += pv * vv.w;
+      }
+    }
+    for (int r = 0; r < dim; ++r) {
+      const float4 t = *reinterpret_cast<const float4*>(s_s + r * GC_COLS + 4 * tx);
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const float qv = q_s[(ty + 16 * a) * DS + r];
+        acc[a][0] += qv * t.x;
+        acc[a][1] += qv * t.y;
+        acc[a][2] += qv * t.z;
+        acc[a][3] += qv * t.w;
+      }
+    }
 #pragma unroll
     for (int a = 0; a < 4; ++a) {
-      const float pv = p_s[(ty + 16 * a) * (GC + 1) + j];
-      acc[a][0] += pv * vv.x;
-      acc[a][1] += pv * vv.y;
-      acc[a][2] += pv * vv.z;
-      acc[a][3] += pv * vv.w;
-    }
-  }
-  __syncthreads();
-  for (int r = 0; r < dim; ++r) {
-    const float4 t = *reinterpret_cast<const float4*>(s_s + r * GC_COLS + 4 * tx);
+      const int i = ty + 16 * a;
+      if (i < n) {
 #pragma unroll
-    for (int a = 0; a < 4; ++a) {
-      const float qv = q_s[(ty + 16 * a) * DS + r];
-      acc[a][0] += qv * t.x;
-      acc[a][1] += qv * t.y;
-      acc[a][2] += qv * t.z;
-      acc[a][3] += qv * t.w;
-    }
-  }
-#pragma unroll
-  for (int a = 0; a < 4; ++a) {
-    const int i = ty + 16 * a;
-    if (i < n) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int col = col0 + 4 * tx + e;
-        if (col < vcols) out[(size_t)(t0 + i) * out_stride + (size_t)h * vcols + col] = acc[a][e];
+        for (int e = 0; e < 4; ++e) {
+          const int col = col0 + 4 * tx + e;
+          if (col < vcols) out[(size_t)(t0 + i) * out_stride + (size_t)h * vcols + col] = acc[a][e];
+        }
       }
     }
   }
@@ -598,7 +606,8 @@ RL_API long long rl_gated_attn_chunked_scratch_floats(int n_seqs, int max_q_len,
 }
 
 static size_t gated_chunk_out_smem(int dim) {
-  return ((size_t)3 * GC * (dim + 1) + GC * GC_COLS + GC * (GC + 1) + 2 * dim) * sizeof(float);
+  const size_t tile = (size_t)GC * (dim + 1), later = (size_t)GC * GC_COLS + GC * (GC + 1);
+  return (2 * tile + (tile > later ? tile : later) + 5 * (size_t)dim) * sizeof(float);
 }
 
 RL_API int rl_gated_attn_chunked_takes(int dim) { return dim > 0 && gated_chunk_out_smem(dim) <= 227 * 1024; }
@@ -616,7 +625,7 @@ RL_API int rl_gated_attn_chunked(const void* q, const void* k, const void* v, in
   if (sh > 0x7fffffffLL || max_chunks > 65535 || col_tiles > 65535) RL_REFUSE(3, "gated_attn_chunked: %d chunks or %d column tiles exceed the grid", max_chunks, col_tiles);
   float* chunk_decay = scratch + sh * max_chunks * dim * vcols;
   const int elems = dim * vcols;
-  dim3 grid((unsigned)sh, max_chunks, col_tiles), grid2((unsigned)sh, (elems + 255) / 256);
+  dim3 grid((unsigned)sh, max_chunks, col_tiles), grid2((unsigned)sh, (elems + 255) / 256), grid3((unsigned)sh, max_chunks);
   const size_t smem1 = ((size_t)GC * dim + GC * GC_COLS) * sizeof(float), smem3 = gated_chunk_out_smem(dim);
 #define RL_GC(T)                                                                                                                     \
   do {                                                                                                                               \
@@ -627,7 +636,7 @@ RL_API int rl_gated_attn_chunked(const void* q, const void* k, const void* v, in
                               per_channel, in_scale, seq_start, scratch, chunk_decay, max_chunks, H, dim, vdim, ext));               \
     RL_LAUNCH_CHECK(rl_launch(gated_chunk_scan_kernel, grid2, 256, 0, stream, state, slot_ids, seq_start, scratch,                   \
                               (const float*)chunk_decay, max_chunks, H, dim, vcols));                                                \
-    RL_LAUNCH_CHECK(rl_launch(gated_chunk_out_kernel<T>, grid, 256, smem3, stream, (const T*)q, (const T*)k, (const T*)v, in_stride,  \
+    RL_LAUNCH_CHECK(rl_launch(gated_chunk_out_kernel<T>, grid3, 256, smem3, stream, (const T*)q, (const T*)k, (const T*)v, in_stride,  \
                               log_decay, per_channel, in_scale, q_scale, seq_start, (const float*)scratch, max_chunks, out,          \
                               out_stride, H, dim, vdim, ext));                                                                       \
   } while (0)
