@@ -104,6 +104,111 @@ __global__ void qkv_prep_kernel(T* __restrict__ qkv, int row_stride, const float
   }
 }
 
+// The same for bfloat16 rows whose sizes are multiples of 8 and whose pairs are neighbours (or that are not rotated at all): a
+// thread takes 8 numbers of a head with one 16-byte load, the kdim / 8 threads of a head add their squares up by shuffles, and
+// the four pairs a thread holds are rotated in its registers; q goes back and k, v go to their pages with 16-byte stores.
+__device__ __forceinline__ void qp_unpack8(const uint4& raw, float* x) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(p[j]);
+    x[2 * j] = f.x;
+    x[2 * j + 1] = f.y;
+  }
+}
+
+__device__ __forceinline__ uint4 qp_pack8(const float* x) {
+  uint4 raw;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) p[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+  return raw;
+}
+
+__device__ __forceinline__ void qp_add8(float* x, const float* b) {
+  const float4 b0 = *reinterpret_cast<const float4*>(b), b1 = *reinterpret_cast<const float4*>(b + 4);
+  x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w;
+  x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
+}
+
+__global__ void __launch_bounds__(256)
+qkv_prep_rows8_kernel(bf16* __restrict__ qkv, int row_stride, const float* __restrict__ bias, const int* __restrict__ tok_pos,
+                      const int* __restrict__ tok_seq, const int* __restrict__ block_table, int table_width,
+                      bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, const float* __restrict__ inv_freq, float magnitude,
+                      const float* __restrict__ q_norm, const float* __restrict__ k_norm, float norm_eps, int H, int K, int kdim,
+                      int vdim, int rot, int page_size) {
+  extern __shared__ float trig[];  // cos[rot/2], sin[rot/2], both times the magnitude
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  const int half = rot >> 1;
+  float* cs = trig;
+  float* sn = trig + half;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    const float a = (float)pos * inv_freq[j];
+    float s, c;
+    sincosf(a, &s, &c);
+    cs[j] = c * magnitude;
+    sn[j] = s * magnitude;
+  }
+  __syncthreads();
+  bf16* row = qkv + (size_t)t * row_stride;
+  const int page = block_table[(size_t)tok_seq[t] * table_width + pos / page_size];
+  const int in_page = pos % page_size;
+  const int g = kdim >> 3;  // threads to a head: a power of two up to 32
+  const int total = (H + K) * g;
+  const bool normed = q_norm != nullptr || k_norm != nullptr;
+  for (int base = 0; base < total; base += blockDim.x) {
+    const int idx = base + threadIdx.x;
+    const bool valid = idx < total;  // (a head's threads are all valid or all not; every lane takes part in the shuffles)
+    const int h = valid ? idx / g : 0, i0 = valid ? (idx - h * g) * 8 : 0;
+    float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (valid) {
+      qp_unpack8(*reinterpret_cast<const uint4*>(row + (size_t)h * kdim + i0), x);
+      if (bias) qp_add8(x, bias + (size_t)h * kdim + i0);
+    }
+    if (normed) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+      for (int o = g >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float* nw = h < H ? q_norm : k_norm;
+      if (valid && nw) {
+        const float inv = 1.0f / sqrtf(ss / (float)kdim + norm_eps);
+        const float4 w0 = *reinterpret_cast<const float4*>(nw + i0), w1 = *reinterpret_cast<const float4*>(nw + i0 + 4);
+        x[0] = x[0] * inv * w0.x; x[1] = x[1] * inv * w0.y; x[2] = x[2] * inv * w0.z; x[3] = x[3] * inv * w0.w;
+        x[4] = x[4] * inv * w1.x; x[5] = x[5] * inv * w1.y; x[6] = x[6] * inv * w1.z; x[7] = x[7] * inv * w1.w;
+      }
+    }
+    if (valid) {
+      if (i0 < rot) {
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const float c = cs[(i0 >> 1) + p], sv = sn[(i0 >> 1) + p];
+          const float a = x[2 * p], b = x[2 * p + 1];
+          x[2 * p] = a * c - b * sv;
+          x[2 * p + 1] = b * c + a * sv;
+        }
+      }
+      bf16* dst = h < H ? row + (size_t)h * kdim + i0 : k_pages + (((size_t)page * K + (h - H)) * page_size + in_page) * kdim + i0;
+      *reinterpret_cast<uint4*>(dst) = qp_pack8(x);
+    }
+  }
+  const bf16* vrow = row + (size_t)(H + K) * kdim;
+  const float* vb = bias ? bias + (size_t)(H + K) * kdim : nullptr;
+  const int gv = vdim >> 3;
+  for (int idx = threadIdx.x; idx < K * gv; idx += blockDim.x) {
+    const int h = idx / gv, i = (idx - h * gv) * 8;
+    uint4 raw = *reinterpret_cast<const uint4*>(vrow + (size_t)h * vdim + i);
+    if (vb) {
+      float x[8];
+      qp_unpack8(raw, x);
+      qp_add8(x, vb + (size_t)h * vdim + i);
+      raw = qp_pack8(x);
+    }
+    *reinterpret_cast<uint4*>(v_pages + (((size_t)page * K + h) * page_size + in_page) * vdim + i) = raw;
+  }
+}
+
 RL_API int rl_qkv_prep(void* qkv, int dtype, int row_stride, const float* bias, const int* tok_pos, const int* tok_seq,
                        const int* block_table, int table_width, void* k_pages, void* v_pages, const float* inv_freq,
                        float magnitude, const float* q_norm, const float* k_norm, float norm_eps, int n_tokens, int H, int K, int kdim,
@@ -117,7 +222,14 @@ RL_API int rl_qkv_prep(void* qkv, int dtype, int row_stride, const float* bias, 
   const size_t smem = ((size_t)rot + H + K) * sizeof(float);
   if (smem > 48 * 1024) RL_REFUSE(6, "qkv_prep: rotary size %d or %d heads too large", rot, H + K);
   const int threads = 256;
-  if (dtype == RL_BF16)
+  const int g = kdim >> 3;
+  const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)bias | (uintptr_t)q_norm | (uintptr_t)k_norm;
+  if (dtype == RL_BF16 && (interleaved || rot == 0) && kdim % 8 == 0 && vdim % 8 == 0 && rot % 8 == 0 && row_stride % 8 == 0 &&
+      g <= 32 && (g & (g - 1)) == 0 && (bits & 15) == 0)
+    qkv_prep_rows8_kernel<<<n_tokens, threads, (size_t)rot * sizeof(float), stream>>>(
+        (bf16*)qkv, row_stride, bias, tok_pos, tok_seq, block_table, table_width, (bf16*)k_pages, (bf16*)v_pages, inv_freq, magnitude,
+        q_norm, k_norm, norm_eps, H, K, kdim, vdim, rot, page_size);
+  else if (dtype == RL_BF16)
     qkv_prep_kernel<bf16><<<n_tokens, threads, smem, stream>>>((bf16*)qkv, row_stride, bias, tok_pos, tok_seq, block_table, table_width,
                                                                (bf16*)k_pages, (bf16*)v_pages, inv_freq, magnitude, q_norm, k_norm, norm_eps, H, K,
                                                                kdim, vdim, rot, interleaved, page_size);

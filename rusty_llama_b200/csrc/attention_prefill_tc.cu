@@ -404,7 +404,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
       tc_fence_after();
       const int key0 = (tile_lo + j) * BNK;
-      const bool need_mask = key0 + BNK - 1 > first_pos || window != 0 || chunk != 0;
+      // (a chunk's start cuts into a tile only where the tile begins before the chunk of the block's last row)
+      const bool need_mask = key0 + BNK - 1 > first_pos || window != 0 || (chunk != 0 && key0 < rl_first_key(last_pos, 0, chunk));
       const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) * BNK);
       // this thread's row of S in one round trip
       uint32_t v[BNK];

@@ -220,3 +220,58 @@ def test_random_scores_in_portions_and_alone(kernel):
         for p0, n in cuts:
             got = attend(kernel, q[p0: p0 + n], kp, vp, pages, p0, H, G, kd, vd, scale, cap, chunk)
             assert np.abs(got - ref[p0: p0 + n]).max() <= _tol(kernel) * max(1.0, np.abs(ref).max()), (H, kd, p0, n)
+
+
+@pytest.mark.parametrize("dtype, H, G, kd, vd, rot, pad", [
+    (torch.bfloat16, 4, 2, 64, 32, 32, 0),     # rows of 16 bytes: eight numbers to a thread, a head's threads add up by shuffles
+    (torch.bfloat16, 3, 1, 128, 128, 128, 8),  # 16 threads to a head; more heads than fill the block's first round evenly
+    (torch.bfloat16, 40, 8, 8, 8, 0, 0),       # one thread to a head, no rotation, two rounds of the block
+    (torch.bfloat16, 2, 2, 16, 24, 8, 3),      # a row stride that is no multiple of 8: the element-wise kernel
+    (torch.float32, 4, 2, 64, 32, 32, 0),
+    (torch.float32, 3, 1, 20, 12, 6, 1),
+])
+def test_biases_norms_of_heads_rotation_and_cache_write(dtype, H, G, kd, vd, rot, pad):
+    """q in place, k and v in shuffled pages, positions around a page border, weights of the norms that differ from 1."""
+    g = torch.Generator().manual_seed(kd + vd)
+    pos = torch.tensor([62, 63, 64, 65, 0, 1, 700])
+    seq = [0, 0, 0, 0, 1, 1, 2]
+    T, cols, eps, base = len(seq), (H + G) * kd + G * vd, 1e-3, 300.0
+    x = torch.randn(T, cols + pad, generator=g, dtype=F64).to(dtype).to(F64)
+    bias = torch.randn(cols, generator=g).to(F64)
+    wq, wk = (torch.rand(kd, generator=g) + 0.5).to(F64), (torch.rand(kd, generator=g) + 0.5).to(F64)
+    freq = (base ** (-2.0 * torch.arange(rot // 2, dtype=F64) / max(rot, 1))).float()
+    table = _i32([[3, 1] + [0] * 9, [2, 0] + [0] * 9, [5] * 10 + [4]])
+    kp = torch.zeros((6, G, 64, kd), dtype=dtype, device="cuda")
+    vp = torch.zeros((6, G, 64, vd), dtype=dtype, device="cuda")
+    xt = x.to("cuda", dtype)
+    from rusty_llama_b200.kernels import ops
+    ops.qkv_prep(xt, bias.float().cuda(), _i32(pos.numpy()), _i32(seq), table, kp, vp, freq.cuda() if rot else None, 1.0, H, G, kd, vd, rot, True,
+                 q_norm=wq.float().cuda(), k_norm=wk.float().cuda(), norm_eps=eps)
+    y = x[:, :cols] + bias
+
+    def plain(heads, w):  # the frequencies as the kernel gets them, rounded to 32 bits
+        heads = pt.rms_norm(heads, w, eps)
+        if not rot:
+            return heads
+        ang = pos.to(F64)[:, None] * freq.to(F64)[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        out = heads.clone()
+        u, w2 = heads[..., 0:rot:2], heads[..., 1:rot:2]
+        out[..., 0:rot:2], out[..., 1:rot:2] = u * c - w2 * s, w2 * c + u * s
+        return out
+
+    q_ref = plain(y[:, : H * kd].reshape(T, H, kd), wq)
+    k_ref = plain(y[:, H * kd: (H + G) * kd].reshape(T, G, kd), wk)
+    v_ref = y[:, (H + G) * kd:].reshape(T, G, vd)
+    tol = 3e-5 if dtype == torch.float32 else 3e-2  # (position 700 times a 32-bit frequency: the angle itself carries 4e-5)
+    got = xt.to(F64).cpu()
+    assert float((got[:, : H * kd].reshape(T, H, kd) - q_ref).abs().max()) <= tol * 4
+    assert torch.equal(got[:, cols:], x[:, cols:])
+    tab = table.cpu()
+    for t in range(T):
+        page = int(tab[seq[t], int(pos[t]) // 64])
+        assert float((kp[page, :, int(pos[t]) % 64].to(F64).cpu() - k_ref[t]).abs().max()) <= tol * 4, t
+        assert float((vp[page, :, int(pos[t]) % 64].to(F64).cpu() - v_ref[t]).abs().max()) <= tol, t
+    used = {int(tab[s, int(p) // 64]) for s, p in zip(seq, pos)}
+    for page in set(range(6)) - used:
+        assert not bool(kp[page].any()) and not bool(vp[page].any())
