@@ -34,10 +34,10 @@ DECAY_RANK = 16
 
 def tefavik_config(z: dict) -> dict:
     H, G, hd = z["heads"], z["kv_heads"], z["hd"]
-    left = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": 1.0 / math.sqrt(hd), "softcap": 50.0, "mask": {"size": z["chunk"]},
+    left = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": 1.0 / math.sqrt(hd), "softcap": 30.0, "mask": {"size": z["chunk"]},
             "rot": {"base": 10000.0, "dims": hd}}
     right = {"heads": z["mem_heads"], "dim": hd, "vdim": hd, "gate_cap": 15.0}
-    gla = {"heads": H, "dim": hd, "vdim": hd, "tau": 16.0}
+    gla = {"heads": H, "dim": hd, "vdim": hd, "tau": 8.0}
     mlp = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["eff"], "limit": 7.0}}
     kinds = [("gla", gla), ("parallel", {"left": left, "right": right})]
     layers = [{"type": t, "mixer": m, "mlp": mlp} for t, m in (kinds[i % 2] for i in range(LAYERS))]
@@ -102,7 +102,7 @@ def kernel_table(z: dict, T: int, batch: int, ctx: int, peaks: dict) -> Dict[str
         nbytes = rows * ((H + G) * hd * 4 + G * hd * 4)
         note(f"{tag}_bias_norm_rotate_store", us, nbytes, 0, like={"kernel": "rope_kv_write", "us": round(us_like, 1), "frac": _frac(us_like, nbytes, 0, peaks)})
         sink = torch.zeros(H, device=dev)
-        run = attention_part.chunked_attention_runner(qkv, kp, vp, table, step, H, G, hd, hd, scale, C, 50.0, sink)
+        run = attention_part.chunked_attention_runner(qkv, kp, vp, table, step, H, G, hd, hd, scale, C, 30.0, sink)
         us = mb._time(lambda i: run(), 1, **it)
         keys = sum(p % C + 1 for p in range(pos0, pos0 + per)) * n_seqs
         seen = min(C, pos0 + per) if prompt else (pos0 % C + 1)
@@ -125,9 +125,9 @@ def kernel_table(z: dict, T: int, batch: int, ctx: int, peaks: dict) -> Dict[str
             else:
                 zz = torch.randn(rows, qd, device=dev, dtype=bf)
                 bz = torch.zeros(qd, device=dev)
-                us = mb._time(lambda i: ops.gla_log_decay(zz, bz, 16.0), 1, **it)
+                us = mb._time(lambda i: ops.gla_log_decay(zz, bz, 8.0), 1, **it)
                 note(f"{tag}_gla_log_decay", us, rows * qd * 6, 0)
-                log_a, b, m = ops.gla_log_decay(zz, bz, 16.0), None, None
+                log_a, b, m = ops.gla_log_decay(zz, bz, 8.0), None, None
             mixer = SimpleNamespace(H=heads, dim=hd, vdim=hd, q_scale=hd ** -0.5, rt=SimpleNamespace(workspace=_Workspace(dev)))
             us = mb._time(lambda i: recurrent_part._recurrence(mixer, q, k, v, log_a, b, state, step, ext), 1, **it)
             like = None
