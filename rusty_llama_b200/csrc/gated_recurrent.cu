@@ -324,6 +324,13 @@ __device__ __forceinline__ float gr_exp2(float x) {
   return y;
 }
 
+// A last column tile of at most four columns (a matrix memory's normaliser beside values that fill whole tiles) gets no block and
+// no round of its own: the block of the tile before it adds those columns up with a thread per (row, quarter of the sum).
+__host__ __device__ __forceinline__ int gc_narrow(int vcols) {
+  const int tiles = (vcols + GC_COLS - 1) / GC_COLS, rem = vcols - (tiles - 1) * GC_COLS;
+  return tiles > 1 && rem <= 4 ? rem : 0;
+}
+
 // (1): grid (S * H, chunks, column tiles), 256 threads: thread (ty, tx) owns rows ty + 16 a and columns 4 tx .. 4 tx + 3.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -340,10 +347,17 @@ gated_chunk_state_kernel(const T* __restrict__ k, const T* __restrict__ v, int i
   if (n <= 0) return;
   float* k_s = sm;             // [GC][dim]: first the decays' logarithms, then the weighted keys
   float* v_s = sm + GC * dim;  // [GC][GC_COLS]
+  float* v_x = v_s + GC * GC_COLS;  // [GC][4]: the narrow last tile's values
+  const int narrow = blockIdx.z == gridDim.z - 1 ? gc_narrow(vcols) : 0;
+  const int col_x0 = (int)gridDim.z * GC_COLS;
   for (int idx = threadIdx.x; idx < n * dim; idx += 256) {
     const int i = idx / dim, r = idx - i * dim;
     const size_t th = (size_t)(t0 + i) * H + h;
     k_s[idx] = GR_LOG2E * (per_channel ? log_decay[th * dim + r] : log_decay[th]);
+  }
+  for (int idx = threadIdx.x; idx < n * narrow; idx += 256) {
+    const int i = idx / narrow, e = idx - i * narrow, cc = col_x0 + e;
+    v_x[i * 4 + e] = cc < vdim ? to_f32(v[(size_t)(t0 + i) * in_stride + (size_t)h * vdim + cc]) : 1.f;
   }
   for (int idx = threadIdx.x; idx < n * GC_COLS; idx += 256) {
     const int i = idx / GC_COLS, cc = col0 + (idx - i * GC_COLS);
@@ -401,6 +415,12 @@ gated_chunk_state_kernel(const T* __restrict__ k, const T* __restrict__ v, int i
         }
       }
     }
+  }
+  for (int idx = threadIdx.x; idx < dim * narrow; idx += 256) {
+    const int r = idx / narrow, e = idx - r * narrow;
+    float acc = 0.f;
+    for (int i = 0; i < n; ++i) acc += k_s[i * dim + r] * v_x[i * 4 + e];
+    u[(size_t)r * vcols + col_x0 + e] = acc;
   }
 }
 
@@ -464,6 +484,12 @@ gated_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
   float* v_s = a_s;                   // [GC][GC_COLS]
   float* p_s = v_s + GC * GC_COLS;    // [GC][GC + 1]
   float* d_s = a_s + max(GC * DS, GC * GC_COLS + GC * (GC + 1));  // [5][dim]: the decay over sub-chunk 1 and over sub-chunk 2; A at the ends of sub-chunks 0, 1, 2
+  float* v_x = d_s + 5 * dim;         // [GC][4]: the narrow last tile's values
+  const int narrow = gc_narrow(vcols), wide_cols = vcols - narrow;
+  for (int idx = threadIdx.x; idx < n * narrow; idx += 256) {
+    const int i = idx / narrow, e = idx - i * narrow, cc = wide_cols + e;
+    v_x[i * 4 + e] = cc < vdim ? to_f32(v[(size_t)(t0 + i) * in_stride + (size_t)h * vdim + cc]) : 1.f;
+  }
   for (int idx = threadIdx.x; idx < GC * dim; idx += 256) {
     const int i = idx / dim, r = idx - i * dim;
     float qv = 0.f, kv = 0.f, la = 0.f;
@@ -546,7 +572,7 @@ gated_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
   }
   const float* sp = scratch + ((size_t)blockIdx.x * max_chunks + c) * dim * vcols;
   float* s_s = k_s;  // [dim][GC_COLS]; GC * (dim + 1) >= dim * GC_COLS
-  for (int col0 = 0; col0 < vcols; col0 += GC_COLS) {
+  for (int col0 = 0; col0 < wide_cols; col0 += GC_COLS) {
     __syncthreads();  // scores and queries written, keys read (first tile); the tile before read
     for (int idx = threadIdx.x; idx < GC * GC_COLS; idx += 256) {
       const int i = idx / GC_COLS, cc = col0 + (idx - i * GC_COLS);
@@ -599,6 +625,32 @@ gated_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
       }
     }
   }
+  if (narrow > 0) {  // thread (i, part): a quarter of row i's sums over the keys and over the state's rows, added up by shuffles
+    const int i = threadIdx.x >> 2, part = threadIdx.x & 3;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = part; j < n; j += 4) {
+      const float pv = p_s[i * (GC + 1) + j];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (e < narrow) acc[e] += pv * v_x[j * 4 + e];
+    }
+    for (int r = part; r < dim; r += 4) {
+      const float qv = q_s[i * DS + r];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (e < narrow) acc[e] += qv * sp[(size_t)r * vcols + wide_cols + e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 1);
+      acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
+    }
+    if (part == 0 && i < n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (e < narrow) out[(size_t)(t0 + i) * out_stride + (size_t)h * vcols + wide_cols + e] = acc[e];
+    }
+  }
 }
 
 RL_API long long rl_gated_attn_chunked_scratch_floats(int n_seqs, int max_q_len, int H, int dim, int vcols) {
@@ -607,7 +659,7 @@ RL_API long long rl_gated_attn_chunked_scratch_floats(int n_seqs, int max_q_len,
 
 static size_t gated_chunk_out_smem(int dim) {
   const size_t tile = (size_t)GC * (dim + 1), later = (size_t)GC * GC_COLS + GC * (GC + 1);
-  return (2 * tile + (tile > later ? tile : later) + 5 * (size_t)dim) * sizeof(float);
+  return (2 * tile + (tile > later ? tile : later) + 5 * (size_t)dim + GC * 4) * sizeof(float);
 }
 
 RL_API int rl_gated_attn_chunked_takes(int dim) { return dim > 0 && gated_chunk_out_smem(dim) <= 227 * 1024; }
@@ -620,13 +672,13 @@ RL_API int rl_gated_attn_chunked(const void* q, const void* k, const void* v, in
     RL_REFUSE(1, "gated_attn_chunked: S=%d max_q=%d H=%d dim=%d vdim=%d ext=%d", n_seqs, max_q_len, H, dim, vdim, ext);
   if (!rl_gated_attn_chunked_takes(dim)) RL_REFUSE(2, "gated_attn_chunked: key size %d needs more shared memory than an SM has", dim);
   const int vcols = vdim + ext;
-  const int max_chunks = (max_q_len + GC - 1) / GC, col_tiles = (vcols + GC_COLS - 1) / GC_COLS;
+  const int max_chunks = (max_q_len + GC - 1) / GC, col_tiles = (vcols + GC_COLS - 1) / GC_COLS - (gc_narrow(vcols) > 0 ? 1 : 0);
   const long long sh = (long long)n_seqs * H;
   if (sh > 0x7fffffffLL || max_chunks > 65535 || col_tiles > 65535) RL_REFUSE(3, "gated_attn_chunked: %d chunks or %d column tiles exceed the grid", max_chunks, col_tiles);
   float* chunk_decay = scratch + sh * max_chunks * dim * vcols;
   const int elems = dim * vcols;
   dim3 grid((unsigned)sh, max_chunks, col_tiles), grid2((unsigned)sh, (elems + 255) / 256), grid3((unsigned)sh, max_chunks);
-  const size_t smem1 = ((size_t)GC * dim + GC * GC_COLS) * sizeof(float), smem3 = gated_chunk_out_smem(dim);
+  const size_t smem1 = ((size_t)GC * dim + GC * GC_COLS + GC * 4) * sizeof(float), smem3 = gated_chunk_out_smem(dim);
 #define RL_GC(T)                                                                                                                     \
   do {                                                                                                                               \
     if (cudaFuncSetAttribute(gated_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1) != cudaSuccess || \

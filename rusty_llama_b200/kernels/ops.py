@@ -1580,7 +1580,7 @@ GATED_CHUNK = 64  # tokens per chunk of the chunked recurrence
 def gated_attn_chunked_takes(dim: int, vcols: int) -> bool:
     """Whether the chunked form of `gated_attn` is built for these sizes (its last kernel keeps three [64, dim + 1] tiles in shared memory)."""
     tile, later = GATED_CHUNK * (dim + 1), GATED_CHUNK * 64 + GATED_CHUNK * (GATED_CHUNK + 1)
-    return dim > 0 and (2 * tile + max(tile, later) + 5 * dim) * 4 <= 227 * 1024
+    return dim > 0 and (2 * tile + max(tile, later) + 5 * dim + GATED_CHUNK * 4) * 4 <= 227 * 1024
 
 
 def gated_attn_chunked_scratch_floats(n_seqs: int, max_q_len: int, num_heads: int, dim: int, vcols: int) -> int:

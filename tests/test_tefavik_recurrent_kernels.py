@@ -80,9 +80,10 @@ def test_log_decay_against_the_plain_formula():
         assert float((got - want).abs().max()) <= tol * (1 + float(want.abs().max()))
 
 
+@pytest.mark.parametrize("H, dim, vdim", [(3, 24, 40), (2, 16, 67), (1, 8, 132)])  # (one column tile; a tile and three columns; two and four)
 @pytest.mark.parametrize("chunked", [False, True])
-def test_gated_linear_attention_in_steps(chunked):
-    H, dim, vdim, lens = 3, 24, 40, [150, 1, 67, 64]
+def test_gated_linear_attention_in_steps(chunked, H, dim, vdim):
+    lens = [150, 1, 67, 64]
     dtype = torch.bfloat16 if chunked else torch.float32
     q, k, v, g = _inputs(sum(lens), H, dim, vdim, 2, dtype)
     log_a = -torch.rand(sum(lens), H * dim, generator=g, dtype=F64) * 0.2
