@@ -16,7 +16,8 @@
 //   - a gate on the result, out *= sigmoid(gate), and a constant factor `out_scale`.
 //
 // Two kernels.  `qkv_prep` adds the biases, rotates q in place and writes the rotated k and v to the token's
-// place in its sequence's pages.  `attn_ext` is the attention itself, for prompts and for decoding, in both
+// place in its sequence's pages; with `v_src` the value that is stored is (1 - lambda) v + lambda v_src[t] (values that an
+// earlier layer projected for the same token; lambda a learned number on the device), computed in 32-bit.  `attn_ext` is the attention itself, for prompts and for decoding, in both
 // element types: one warp per (token, head), the keys taken 32 at a time counted from the first key the
 // query may see, online softmax, every sum in 32-bit and in a fixed order, so a result's bits depend neither
 // on how its sequence was cut into steps nor on what else is in the batch.  With a mixing matrix the warps
@@ -36,7 +37,8 @@ __global__ void qkv_prep_kernel(T* __restrict__ qkv, int row_stride, const float
                                 const int* __restrict__ block_table, int table_width, T* __restrict__ k_pages,
                                 T* __restrict__ v_pages, const float* __restrict__ inv_freq, float magnitude,
                                 const float* __restrict__ q_norm, const float* __restrict__ k_norm, float norm_eps, int H, int K,
-                                int kdim, int vdim, int rot, int interleaved, int page_size) {
+                                int kdim, int vdim, int rot, int interleaved, int page_size, const T* __restrict__ v_src,
+                                int v_src_stride, const float* __restrict__ v_lambda) {
   extern __shared__ float trig[];  // cos[rot/2], sin[rot/2], both times the magnitude; then 1 / rms of every q and k head
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
@@ -98,9 +100,13 @@ __global__ void qkv_prep_kernel(T* __restrict__ qkv, int row_stride, const float
   }
   const T* vrow = row + (size_t)(H + K) * kdim;
   const float* vb = bias ? bias + (size_t)(H + K) * kdim : nullptr;
+  const float lam = v_src ? v_lambda[0] : 0.f;
+  const T* vs = v_src ? v_src + (size_t)t * v_src_stride : nullptr;
   for (int idx = threadIdx.x; idx < K * vdim; idx += blockDim.x) {
     const int h = idx / vdim, i = idx - h * vdim;
-    v_pages[(((size_t)page * K + h) * page_size + in_page) * vdim + i] = from_f32<T>(to_f32(vrow[idx]) + (vb ? vb[idx] : 0.f));
+    float v = to_f32(vrow[idx]) + (vb ? vb[idx] : 0.f);
+    if (vs) v = (1.0f - lam) * v + lam * to_f32(vs[idx]);
+    v_pages[(((size_t)page * K + h) * page_size + in_page) * vdim + i] = from_f32<T>(v);
   }
 }
 
@@ -136,7 +142,8 @@ qkv_prep_rows8_kernel(bf16* __restrict__ qkv, int row_stride, const float* __res
                       const int* __restrict__ tok_seq, const int* __restrict__ block_table, int table_width,
                       bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, const float* __restrict__ inv_freq, float magnitude,
                       const float* __restrict__ q_norm, const float* __restrict__ k_norm, float norm_eps, int H, int K, int kdim,
-                      int vdim, int rot, int page_size) {
+                      int vdim, int rot, int page_size, const bf16* __restrict__ v_src, int v_src_stride,
+                      const float* __restrict__ v_lambda) {
   extern __shared__ float trig[];  // cos[rot/2], sin[rot/2], both times the magnitude
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
@@ -199,10 +206,17 @@ qkv_prep_rows8_kernel(bf16* __restrict__ qkv, int row_stride, const float* __res
   for (int idx = threadIdx.x; idx < K * gv; idx += blockDim.x) {
     const int h = idx / gv, i = (idx - h * gv) * 8;
     uint4 raw = *reinterpret_cast<const uint4*>(vrow + (size_t)h * vdim + i);
-    if (vb) {
+    if (vb || v_src) {
       float x[8];
       qp_unpack8(raw, x);
-      qp_add8(x, vb + (size_t)h * vdim + i);
+      if (vb) qp_add8(x, vb + (size_t)h * vdim + i);
+      if (v_src) {
+        const float lam = v_lambda[0];
+        float y[8];
+        qp_unpack8(*reinterpret_cast<const uint4*>(v_src + (size_t)t * v_src_stride + (size_t)h * vdim + i), y);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = (1.0f - lam) * x[j] + lam * y[j];
+      }
       raw = qp_pack8(x);
     }
     *reinterpret_cast<uint4*>(v_pages + (((size_t)page * K + h) * page_size + in_page) * vdim + i) = raw;
@@ -212,7 +226,9 @@ qkv_prep_rows8_kernel(bf16* __restrict__ qkv, int row_stride, const float* __res
 RL_API int rl_qkv_prep(void* qkv, int dtype, int row_stride, const float* bias, const int* tok_pos, const int* tok_seq,
                        const int* block_table, int table_width, void* k_pages, void* v_pages, const float* inv_freq,
                        float magnitude, const float* q_norm, const float* k_norm, float norm_eps, int n_tokens, int H, int K, int kdim,
-                       int vdim, int rot, int interleaved, int page_size, cudaStream_t stream) {
+                       int vdim, int rot, int interleaved, int page_size, const void* v_src, int v_src_stride, const float* v_lambda,
+                       cudaStream_t stream) {
+  if (v_src != nullptr && (v_lambda == nullptr || v_src_stride < K * vdim)) RL_REFUSE(8, "qkv_prep: values to mix in need a factor and rows of %d numbers", K * vdim);
   if (n_tokens <= 0 || H <= 0 || K <= 0 || kdim <= 0 || vdim <= 0 || page_size <= 0 || table_width <= 0)
     RL_REFUSE(1, "qkv_prep: T=%d H=%d K=%d kdim=%d vdim=%d page=%d", n_tokens, H, K, kdim, vdim, page_size);
   if (rot < 0 || rot > kdim || (rot & 1)) RL_REFUSE(2, "qkv_prep: %d rotated dimensions do not fit a head of %d", rot, kdim);
@@ -223,20 +239,21 @@ RL_API int rl_qkv_prep(void* qkv, int dtype, int row_stride, const float* bias, 
   if (smem > 48 * 1024) RL_REFUSE(6, "qkv_prep: rotary size %d or %d heads too large", rot, H + K);
   const int threads = 256;
   const int g = kdim >> 3;
-  const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)bias | (uintptr_t)q_norm | (uintptr_t)k_norm;
+  const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)bias | (uintptr_t)q_norm | (uintptr_t)k_norm |
+                         (uintptr_t)v_src;
   if (dtype == RL_BF16 && (interleaved || rot == 0) && kdim % 8 == 0 && vdim % 8 == 0 && rot % 8 == 0 && row_stride % 8 == 0 &&
-      g <= 32 && (g & (g - 1)) == 0 && (bits & 15) == 0)
+      v_src_stride % 8 == 0 && g <= 32 && (g & (g - 1)) == 0 && (bits & 15) == 0)
     qkv_prep_rows8_kernel<<<n_tokens, threads, (size_t)rot * sizeof(float), stream>>>(
         (bf16*)qkv, row_stride, bias, tok_pos, tok_seq, block_table, table_width, (bf16*)k_pages, (bf16*)v_pages, inv_freq, magnitude,
-        q_norm, k_norm, norm_eps, H, K, kdim, vdim, rot, page_size);
+        q_norm, k_norm, norm_eps, H, K, kdim, vdim, rot, page_size, (const bf16*)v_src, v_src_stride, v_lambda);
   else if (dtype == RL_BF16)
     qkv_prep_kernel<bf16><<<n_tokens, threads, smem, stream>>>((bf16*)qkv, row_stride, bias, tok_pos, tok_seq, block_table, table_width,
                                                                (bf16*)k_pages, (bf16*)v_pages, inv_freq, magnitude, q_norm, k_norm, norm_eps, H, K,
-                                                               kdim, vdim, rot, interleaved, page_size);
+                                                               kdim, vdim, rot, interleaved, page_size, (const bf16*)v_src, v_src_stride, v_lambda);
   else if (dtype == RL_F32)
     qkv_prep_kernel<float><<<n_tokens, threads, smem, stream>>>((float*)qkv, row_stride, bias, tok_pos, tok_seq, block_table, table_width,
                                                                 (float*)k_pages, (float*)v_pages, inv_freq, magnitude, q_norm, k_norm, norm_eps, H, K,
-                                                                kdim, vdim, rot, interleaved, page_size);
+                                                                kdim, vdim, rot, interleaved, page_size, (const float*)v_src, v_src_stride, v_lambda);
   else
     RL_REFUSE(7, "qkv_prep: unknown dtype %d", dtype);
   RL_LAUNCH_RESULT();

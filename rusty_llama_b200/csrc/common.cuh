@@ -99,7 +99,10 @@ __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat1
 
 // What a gated feed-forward makes of its two 32-bit sums g (gate) and u (up).  limit <= 0: silu(g) * u.
 // limit > 0: g' * logistic(alpha * g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+// limit == RL_GATED_GELU_TANH: gelu(g) * u with the tanh form 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+#define RL_GATED_GELU_TANH (-3.0f)
 __device__ __forceinline__ float gated_act(float g, float u, float alpha, float limit) {
+  if (limit == RL_GATED_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
   if (limit > 0.f) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit) + 1.0f;
@@ -109,6 +112,10 @@ __device__ __forceinline__ float gated_act(float g, float u, float alpha, float 
 }
 // the same with the hardware's approximations of exp and of the division (a few units in the last place of 32 bits)
 __device__ __forceinline__ float gated_act_fast(float g, float u, float alpha, float limit) {
+  if (limit == RL_GATED_GELU_TANH) {  // 0.5 (1 + tanh(z)) = 1 / (1 + exp(-2 z))
+    const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return __fdividef(g, 1.0f + __expf(-2.0f * z)) * u;
+  }
   if (limit > 0.f) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit) + 1.0f;

@@ -14,10 +14,11 @@
 RL_DEFINE_ERROR_TEXT()
 
 // ---------------------------------------------------------------- embedding
-// out[t, :] = table[tokens[t], :] widened to 32-bit, no scale (src/model.rs:1237-1242).
+// out[t, :] = table[tokens[t], :] widened to 32-bit (src/model.rs:1237-1242), times `scale` (1 for a plain copy; a design
+// that multiplies its embedding by a constant does so here, in 32-bit).
 template <typename TW, bool VEC>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
-                                    float* __restrict__ out, int d) {
+                                    float* __restrict__ out, int d, float scale) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -27,10 +28,12 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const TW* __
     for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
       float v[4];
       load4_g<TW>(row + i, v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] *= scale;
       store4<float>(o + i, v);
     }
   } else {
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
   }
 }
 
@@ -40,17 +43,17 @@ static int row_threads(int d) {
 }
 
 RL_API int rl_embed_gather(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens,
-                           int d, cudaStream_t stream) {
+                           int d, float scale, cudaStream_t stream) {
   if (n_tokens <= 0 || d <= 0) RL_REFUSE(1, "embed_gather: n_tokens=%d d=%d", n_tokens, d);
   const int th = row_threads(d);
   if (table_dtype == RL_BF16 && d % 4 == 0)
-    RL_LAUNCH_CHECK(rl_launch(embed_gather_kernel<bf16, true>, n_tokens, th, 0, stream, tokens, (const bf16*)table, out, d));
+    RL_LAUNCH_CHECK(rl_launch(embed_gather_kernel<bf16, true>, n_tokens, th, 0, stream, tokens, (const bf16*)table, out, d, scale));
   else if (table_dtype == RL_BF16)
-    RL_LAUNCH_CHECK(rl_launch<false>(embed_gather_kernel<bf16, false>, n_tokens, 256, 0, stream, tokens, (const bf16*)table, out, d));
+    RL_LAUNCH_CHECK(rl_launch<false>(embed_gather_kernel<bf16, false>, n_tokens, 256, 0, stream, tokens, (const bf16*)table, out, d, scale));
   else if (table_dtype == RL_F32 && d % 4 == 0)
-    RL_LAUNCH_CHECK(rl_launch(embed_gather_kernel<float, true>, n_tokens, th, 0, stream, tokens, (const float*)table, out, d));
+    RL_LAUNCH_CHECK(rl_launch(embed_gather_kernel<float, true>, n_tokens, th, 0, stream, tokens, (const float*)table, out, d, scale));
   else if (table_dtype == RL_F32)
-    RL_LAUNCH_CHECK(rl_launch<false>(embed_gather_kernel<float, false>, n_tokens, 256, 0, stream, tokens, (const float*)table, out, d));
+    RL_LAUNCH_CHECK(rl_launch<false>(embed_gather_kernel<float, false>, n_tokens, 256, 0, stream, tokens, (const float*)table, out, d, scale));
   else
     RL_REFUSE(2, "embed_gather: unknown table dtype %d", table_dtype);
   return 0;
@@ -408,9 +411,7 @@ __global__ void clamped_glu_kernel(const TA* __restrict__ gu, TA* __restrict__ h
   for (; idx < total; idx += step) {
     const long long t = idx / ff;
     const int i = (int)(idx - t * ff);
-    const float g = fminf(to_f32(gu[t * 2 * ff + i]), limit);
-    const float u = fminf(fmaxf(to_f32(gu[t * 2 * ff + ff + i]), -limit), limit);
-    h[idx] = from_f32<TA>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+    h[idx] = from_f32<TA>(gated_act(to_f32(gu[t * 2 * ff + i]), to_f32(gu[t * 2 * ff + ff + i]), alpha, limit));
   }
 }
 

@@ -1,8 +1,9 @@
 // A routed feed-forward: every token is sent to `top` of E small gated feed-forwards.
 //
-//   moe_router   z = W_r x in 32-bit, s = softmax(z) over all experts; the `top` experts with the largest
-//                s + bias are chosen (ties to the lower index), their weights are their s (optionally divided by
-//                their sum); one more row of W_r, if present, gives a per-token gate sigmoid(w_g . x)
+//   moe_router   z = W_r x in 32-bit, s = softmax(z) over all experts (or s = logistic(z), each expert on its own); the
+//                `top` experts with the largest s + bias are chosen (ties to the lower index), their weights are their s
+//                (optionally divided by their sum plus a small constant), times a constant factor; one more row of W_r,
+//                if present, gives a per-token gate sigmoid(w_g . x)
 //   moe_plan     counts the (token, choice) pairs of each expert, lays them out expert after expert (`order`,
 //                with the inverse `place`), and cuts each expert's range into row tiles (`tiles`) of a given height
 //   moe_gemm     one kernel for all experts: a block takes one row tile (rows of ONE expert) and one column
@@ -88,10 +89,11 @@ __global__ void moe_router_logits_kernel(const T* __restrict__ x, int ldx, const
     }
 }
 
-// One warp per token (four tokens per block): softmax over the E logits, the `top` largest of score + bias.
+// One warp per token (four tokens per block): softmax over the E logits (or the logistic function of each), the `top` largest of
+// score + bias; weights s_e (/ (sum of the chosen s + renorm_eps) if renorm) * weight_scale.
 __global__ void moe_router_choose_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int E, int rows, int top,
                                          int renorm, int n_tokens, int* __restrict__ ids, float* __restrict__ weights,
-                                         float* __restrict__ gate) {
+                                         float* __restrict__ gate, int logistic, float renorm_eps, float weight_scale) {
   extern __shared__ float sm[];  // per warp: E scores, E choice scores
   pdl_trigger();
   pdl_wait();
@@ -101,14 +103,15 @@ __global__ void moe_router_choose_kernel(const float* __restrict__ logits, const
   float* z = sm + (size_t)warp * 2 * E;
   float* choice = z + E;
   const float* lg = logits + (size_t)t * rows;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) sum += expf(lg[e] - mx);
-  sum = warp_sum(sum);
+  float mx = -INFINITY, sum = 0.f;
+  if (!logistic) {
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+    mx = warp_max(mx);
+    for (int e = lane; e < E; e += 32) sum += expf(lg[e] - mx);
+    sum = warp_sum(sum);
+  }
   for (int e = lane; e < E; e += 32) {
-    const float s = expf(lg[e] - mx) / sum;
+    const float s = logistic ? 1.0f / (1.0f + expf(-lg[e])) : expf(lg[e] - mx) / sum;
     z[e] = s;
     choice[e] = s + (bias ? bias[e] : 0.f);
   }
@@ -139,14 +142,19 @@ __global__ void moe_router_choose_kernel(const float* __restrict__ logits, const
     chosen_sum += z[at];
     __syncwarp();
   }
-  if (renorm && lane == 0)
-    for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= chosen_sum;
+  if (lane == 0 && (renorm || weight_scale != 1.0f))
+    for (int j = 0; j < top; ++j) {
+      float wj = weights[(size_t)t * top + j];
+      if (renorm) wj /= (chosen_sum + renorm_eps);
+      weights[(size_t)t * top + j] = wj * weight_scale;
+    }
   if (rows > E && lane == 0) gate[t] = 1.0f / (1.0f + expf(-lg[E]));
 }
 
 // logits: float32 scratch of n_tokens * (E + has_gate) values.
 RL_API int rl_moe_router(const void* x, int ldx, int dtype, const float* w, const float* bias, int n_tokens, int E, int d,
-                         int top, int renorm, int has_gate, float* logits, int* ids, float* weights, float* gate, cudaStream_t stream) {
+                         int top, int renorm, int has_gate, float* logits, int* ids, float* weights, float* gate, int logistic,
+                         float renorm_eps, float weight_scale, cudaStream_t stream) {
   if (n_tokens <= 0 || E <= 0 || d <= 0 || top <= 0 || top > E) RL_REFUSE(1, "moe_router: T=%d E=%d d=%d top=%d", n_tokens, E, d, top);
   if (has_gate && gate == nullptr) RL_REFUSE(2, "moe_router: a gate row but nowhere to write the gate");
   const size_t smem = (size_t)4 * 2 * E * sizeof(float);
@@ -167,7 +175,7 @@ RL_API int rl_moe_router(const void* x, int ldx, int dtype, const float* w, cons
   else
     RL_REFUSE(4, "moe_router: unknown dtype %d", dtype);
   RL_LAUNCH_CHECK(rl_launch<false>(moe_router_choose_kernel, (n_tokens + 3) / 4, 128, smem, stream, (const float*)logits, bias, E, rows, top,
-                                   renorm, n_tokens, ids, weights, gate));
+                                   renorm, n_tokens, ids, weights, gate, logistic, renorm_eps, weight_scale));
   return 0;
 }
 

@@ -48,7 +48,10 @@ class StepContext:
     tokens[T], tok_seq[T] (index of the token's sequence in the batch), tok_pos[T]
     (position in its sequence), seq_start[S+1] (offsets of the sequences' tokens),
     seq_pos0[S] (positions held before the step), seq_len[S] (positions held after),
-    slot_ids[S], rows[W] (packed indices of the tokens whose logits are wanted)."""
+    slot_ids[S], rows[W] (packed indices of the tokens whose logits are wanted).
+
+    shared: what one run of the schedule leaves for later runs of the same step (a mixer that hands the values it projected
+    to the layers after it); the model empties it before the first run."""
 
     n_tokens: int
     n_seqs: int
@@ -66,6 +69,7 @@ class StepContext:
     seq_len: torch.Tensor
     slot_ids: torch.Tensor
     rows: Optional[torch.Tensor]
+    shared: Dict[str, torch.Tensor] = field(default_factory=dict)
 
 
 def _pad4(n: int) -> int:

@@ -85,8 +85,8 @@ def _check(lib, rc: int, name: str, kernels: int = 1) -> None:
 
 
 # ------------------------------------------------------------------ row kernels
-def embed_gather(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t] = table[tokens[t]] as float32.  Token ids must already be known to lie in the table."""
+def embed_gather(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = table[tokens[t]] * scale as float32.  Token ids must already be known to lie in the table."""
     _cuda(tokens, "embed_gather tokens", torch.int32)
     _cuda(table, "embed_gather table")
     _need(tokens.dim() == 1 and table.dim() == 2, "embed_gather: tokens[T] and table[V, d] expected")
@@ -97,7 +97,7 @@ def embed_gather(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.
     _need(tuple(out.shape) == (T, d), "embed_gather: out has the wrong shape")
     _need(table.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0, "embed_gather: tensors must be 16-byte aligned")
     lib = build.load("elementwise")
-    rc = lib.rl_embed_gather(_p(tokens), _p(table), c_int(_dt(table, "embed_gather table")), _p(out), c_int(T), c_int(d), _stream())
+    rc = lib.rl_embed_gather(_p(tokens), _p(table), c_int(_dt(table, "embed_gather table")), _p(out), c_int(T), c_int(d), c_float(scale), _stream())
     _check(lib, rc, "embed_gather")
     return out
 
@@ -519,6 +519,8 @@ def _act(act):
         return c_float(1.0), c_float(0.0)
     if act == "relu2":
         return c_float(0.0), c_float(-2.0)
+    if act == "gelu_tanh":  # gelu(gate) * up, the tanh form (RL_GATED_GELU_TANH of csrc/common.cuh)
+        return c_float(0.0), c_float(-3.0)
     alpha, limit = act
     _need(limit > 0, f"a gated activation with limits needs a positive limit, got {limit}")
     return c_float(alpha), c_float(limit)
@@ -948,6 +950,13 @@ def normed_add_rmsnorm(
     return out
 
 
+def gated_glu(gate_up: torch.Tensor, act) -> torch.Tensor:
+    """h[t, i] = act(gate_up[t, i], gate_up[t, ff + i]) for the activations of a gate/up product (None: silu(gate) * up,
+    (alpha, limit): the clamped form, "gelu_tanh": gelu(gate) * up), as a pass of its own behind a plain product."""
+    alpha, limit = _act(act)
+    return clamped_glu(gate_up, alpha.value, limit.value)
+
+
 def clamped_glu(gate_up: torch.Tensor, alpha: float, limit: float) -> torch.Tensor:
     """h[t, i] = g * sigmoid(alpha * g) * (u + 1), g = min(gate_up[t, i], limit), u = clamp(gate_up[t, ff + i], -limit, limit)."""
     _cuda(gate_up, "clamped_glu input")
@@ -1083,11 +1092,13 @@ def moe_tile_rows() -> int:
     return int(build.load("moe").rl_moe_tile_rows())
 
 
-def moe_router(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], n_experts: int, top: int, renormalize: bool = False):
+def moe_router(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], n_experts: int, top: int, renormalize: bool = False,
+               logistic: bool = False, renorm_eps: float = 0.0, weight_scale: float = 1.0):
     """x[T, d], w float32 [E (+1), d] -> (ids int32 [T, top], weights float32 [T, top], gate float32 [T] or None).
 
-    Softmax over the E experts in 32-bit; the `top` largest of score + bias are chosen, their weights are their scores
-    (divided by their sum if `renormalize`).  A row E of w gives gate = sigmoid(w[E] . x)."""
+    Softmax over the E experts in 32-bit (`logistic`: the logistic function of every logit instead); the `top` largest of
+    score + bias are chosen, their weights are their scores (divided by their sum + `renorm_eps` if `renormalize`), times
+    `weight_scale`.  A row E of w gives gate = sigmoid(w[E] . x)."""
     _cuda(x, "moe_router x", contiguous=False)
     _cuda(w, "moe_router w", torch.float32)
     T, d = x.shape
@@ -1103,7 +1114,8 @@ def moe_router(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], n
     lib = build.load("moe")
     rc = lib.rl_moe_router(
         _p(x), c_int(_rows(x, "moe_router x")), c_int(_dt(x, "moe_router")), _p(w), _p(bias), c_int(T), c_int(n_experts), c_int(d), c_int(top),
-        c_int(1 if renormalize else 0), c_int(1 if has_gate else 0), _p(logits), _p(ids), _p(weights), _p(gate), _stream(),
+        c_int(1 if renormalize else 0), c_int(1 if has_gate else 0), _p(logits), _p(ids), _p(weights), _p(gate), c_int(1 if logistic else 0),
+        c_float(renorm_eps), c_float(weight_scale), _stream(),
     )
     _check(lib, rc, "moe_router", kernels=2)
     return ids, weights, gate
@@ -1279,12 +1291,14 @@ def qkv_prep(
     qkv: torch.Tensor, bias: Optional[torch.Tensor], tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
     k_pages: torch.Tensor, v_pages: torch.Tensor, inv_freq: Optional[torch.Tensor], magnitude: float, num_heads: int, num_kv_heads: int,
     kdim: int, vdim: int, rotary_dim: int, interleaved: bool, q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None,
-    norm_eps: float = 0.0,
+    norm_eps: float = 0.0, v_src: Optional[torch.Tensor] = None, v_lambda: Optional[torch.Tensor] = None,
 ) -> None:
     """qkv[T, >= (H + K) kdim + K vdim]: add `bias` (float32, one number per column, or None), divide every q head (k head) by its
     root mean square and multiply it by `q_norm` (`k_norm`; float32 [kdim], None: no norm), rotate the first `rotary_dim`
     dimensions of every q head (in place) and k head by position * inv_freq, cosines and sines times `magnitude`, and store
-    k and v at each token's place in the paged cache (k_pages [pages, K, PAGE_SIZE, kdim], v_pages [..., vdim])."""
+    k and v at each token's place in the paged cache (k_pages [pages, K, PAGE_SIZE, kdim], v_pages [..., vdim]).
+    v_src ([T, K vdim] rows of qkv's type) with v_lambda (float32, one number on the device): what is stored as the value is
+    (1 - lambda) v + lambda v_src[t]."""
     _cuda(qkv, "qkv_prep qkv", contiguous=False)
     stride = _rows(qkv, "qkv_prep qkv")
     T = qkv.shape[0]
@@ -1306,11 +1320,19 @@ def qkv_prep(
         if w is not None:
             _cuda(w, f"qkv_prep {name}", torch.float32)
             _need(w.numel() == kdim, f"qkv_prep: {name} must hold one weight per number of a head ({kdim})")
+    vs_stride = 0
+    if v_src is not None:
+        _cuda(v_src, "qkv_prep v_src", qkv.dtype, contiguous=False)
+        vs_stride = _rows(v_src, "qkv_prep v_src")
+        _need(tuple(v_src.shape) == (T, num_kv_heads * vdim), f"qkv_prep: v_src {tuple(v_src.shape)} is not [T, {num_kv_heads * vdim}]")
+        _cuda(v_lambda, "qkv_prep v_lambda", torch.float32)
+        _need(v_lambda.numel() == 1, "qkv_prep: v_lambda is one number")
     lib = build.load("attention_ext")
     rc = lib.rl_qkv_prep(
         _p(qkv), c_int(_dt(qkv, "qkv_prep")), c_int(stride), _p(bias), _p(tok_pos), _p(tok_seq), _p(block_table), c_int(block_table.shape[1]),
         _p(k_pages), _p(v_pages), _p(inv_freq if rotary_dim else None), c_float(magnitude), _p(q_norm), _p(k_norm), c_float(norm_eps), c_int(T), c_int(num_heads),
-        c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(rotary_dim), c_int(1 if interleaved else 0), c_int(PAGE_SIZE), _stream(),
+        c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(rotary_dim), c_int(1 if interleaved else 0), c_int(PAGE_SIZE),
+        _p(v_src), c_int(vs_stride), _p(v_lambda), _stream(),
     )
     _check(lib, rc, "qkv_prep")
 
@@ -1359,6 +1381,52 @@ def attn_ext(
         c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(PAGE_SIZE), c_int(window), c_float(scale), c_int(chunk), c_float(softcap), _stream(),
     )
     _check(lib, rc, "attn_ext")
+    return out
+
+
+def sigmoid_attn(
+    q: torch.Tensor, k_pages, v_pages, block_table, tok_seq, tok_pos, num_heads: int, num_kv_heads: int, kdim: int, vdim: int,
+    scale: float, head_bias: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+    softcap: float = 0.0, window: int = 0, chunk: int = 0, out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Attention without a softmax: a visible key's weight is logistic(cap(q . k * scale) + head_bias[h]), nothing is normalised
+    over the keys; the heads' weights are mixed by `mix` (w'_h = sum_g mix[h][g] w_g) before head h applies them to the values of
+    its kv head; the result of head h is multiplied by logistic(gate[t, h]) and `out_scale`.  Both element types, prompts and
+    single tokens, every size; each output is one 32-bit sum in a fixed order.
+
+    q: [T, >= H kdim] rows.  head_bias: float32 [H] or None.  mix: float32 [H, H] or None.  gate: [T, >= H] rows of q's type or
+    None.  window, chunk, softcap: as in `attn_ext`.  out: [T, H vdim] rows (a strided view is taken as it is)."""
+    _cuda(q, "sigmoid_attn q", contiguous=False)
+    qs = _rows(q, "sigmoid_attn q")
+    T = q.shape[0]
+    _need(q.shape[1] >= num_heads * kdim, "sigmoid_attn: q rows too short")
+    _check_kv_pages(k_pages, v_pages, q.dtype, num_kv_heads, kdim, vdim, "sigmoid_attn")
+    _cuda(block_table, "sigmoid_attn block_table", torch.int32)
+    _cuda(tok_seq, "sigmoid_attn tok_seq", torch.int32)
+    _cuda(tok_pos, "sigmoid_attn tok_pos", torch.int32)
+    _need(tok_seq.numel() == T and tok_pos.numel() == T and block_table.dim() == 2, "sigmoid_attn: metadata sizes")
+    if head_bias is not None:
+        _cuda(head_bias, "sigmoid_attn head_bias", torch.float32)
+        _need(head_bias.numel() == num_heads, "sigmoid_attn: one bias per head")
+    if mix is not None:
+        _cuda(mix, "sigmoid_attn mix", torch.float32)
+        _need(tuple(mix.shape) == (num_heads, num_heads), "sigmoid_attn: the mixing matrix must be [H, H]")
+    gs = 0
+    if gate is not None:
+        _cuda(gate, "sigmoid_attn gate", q.dtype, contiguous=False)
+        gs = _rows(gate, "sigmoid_attn gate")
+        _need(gate.shape[0] == T and gate.shape[1] >= num_heads, "sigmoid_attn: gate rows too short")
+    if out is None:
+        out = torch.empty((T, num_heads * vdim), dtype=q.dtype, device=q.device)
+    _cuda(out, "sigmoid_attn out", q.dtype, contiguous=False)
+    _need(_rows(out, "sigmoid_attn out") >= num_heads * vdim and tuple(out.shape) == (T, num_heads * vdim), "sigmoid_attn: out must be [T, H vdim]")
+    lib = build.load("attention_sigmoid")
+    rc = lib.rl_sigmoid_attn(
+        _p(q), c_int(_dt(q, "sigmoid_attn")), c_int(qs), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]), _p(tok_seq),
+        _p(tok_pos), _p(head_bias), _p(mix), _p(gate), c_int(gs), c_float(out_scale), _p(out), c_int(out.stride(0)), c_int(T), c_int(num_heads),
+        c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(PAGE_SIZE), c_int(window), c_float(scale), c_int(chunk), c_float(softcap), _stream(),
+    )
+    _check(lib, rc, "sigmoid_attn")
     return out
 
 
@@ -1668,6 +1736,103 @@ def head_norm_gate(
     _check(lib, rc, "head_norm_gate")
     return out
 
+
+
+# ------------------------------------------------------------------ gated delta rule (csrc/delta_rule.cu)
+SHORT_CONV_MAX_TAPS = 16
+DELTA_RULE_MAX_DIM = 256
+
+
+def short_conv(
+    x: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], slot_ids: torch.Tensor, seq_start: torch.Tensor, tok_seq: torch.Tensor,
+    silu: bool = True,
+) -> torch.Tensor:
+    """y[t, c] = act(sum_i w[c, i] x[t - taps + 1 + i, c]) over each sequence's tokens, a causal convolution over time per channel.
+
+    x: [T, C] rows (a view of a projection's rows is taken as it is).  w: float32 [C, taps], the last column the current token's.
+    state: float32 [slots, taps - 1, C], the last taps - 1 inputs of every sequence before this step (zeros at a sequence's
+    start); it is moved on to the end of the step's tokens.  Returns [T, C] in x's type."""
+    _cuda(x, "short_conv x", contiguous=False)
+    xs = _rows(x, "short_conv x")
+    T, C = x.shape
+    _cuda(w, "short_conv w", torch.float32)
+    _need(w.dim() == 2 and w.shape[0] == C, f"short_conv: w {tuple(w.shape)} does not have {C} rows")
+    taps = w.shape[1]
+    _need(1 <= taps <= SHORT_CONV_MAX_TAPS, f"short_conv: {taps} taps (1 to {SHORT_CONV_MAX_TAPS})")
+    _cuda(slot_ids, "short_conv slot_ids", torch.int32)
+    _cuda(seq_start, "short_conv seq_start", torch.int32)
+    _cuda(tok_seq, "short_conv tok_seq", torch.int32)
+    S = slot_ids.numel()
+    _need(seq_start.numel() == S + 1 and tok_seq.numel() == T, "short_conv: metadata sizes")
+    if taps > 1:
+        _cuda(state, "short_conv state", torch.float32)
+        _need(state.dim() == 3 and tuple(state.shape[1:]) == (taps - 1, C), f"short_conv: state {tuple(state.shape)} is not [slots, {taps - 1}, {C}]")
+    out = torch.empty((T, C), dtype=x.dtype, device=x.device)
+    lib = build.load("delta_rule")
+    rc = lib.rl_short_conv(
+        _p(x), c_int(_dt(x, "short_conv")), c_int(xs), _p(w), _p(state if taps > 1 else None), _p(slot_ids), _p(seq_start), _p(tok_seq), _p(out),
+        c_int(out.stride(0)), c_int(T), c_int(S), c_int(C), c_int(taps), c_int(1 if silu else 0), _stream(),
+    )
+    _check(lib, rc, "short_conv", kernels=2 if taps > 1 else 1)
+    return out
+
+
+def delta_prep(
+    qk: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, num_qk_heads: int, num_heads: int, dim: int,
+    unit_eps: float, q_scale: float,
+):
+    """What the gated delta rule's recurrence takes, all float32: qk [T, 2 G dim] rows (G q heads, then G k heads) -> unit vectors
+    qn (times q_scale) and kn [T, G dim], their products kq [T, G]; ba [T, >= 2 H] rows (b, then a) -> beta = logistic(b) and
+    decay = exp(-exp(a_log) softplus(a + dt_bias)), both [T, H]."""
+    _cuda(qk, "delta_prep qk", contiguous=False)
+    _cuda(ba, "delta_prep ba", qk.dtype, contiguous=False)
+    T = qk.shape[0]
+    G, H = num_qk_heads, num_heads
+    _need(qk.shape[1] == 2 * G * dim and ba.shape[0] == T and ba.shape[1] >= 2 * H, "delta_prep: row sizes")
+    _cuda(a_log, "delta_prep a_log", torch.float32)
+    _cuda(dt_bias, "delta_prep dt_bias", torch.float32)
+    _need(a_log.numel() == H and dt_bias.numel() == H, "delta_prep: one A_log and one dt_bias per head")
+    f32 = dict(dtype=torch.float32, device=qk.device)
+    qn, kn = torch.empty((T, G * dim), **f32), torch.empty((T, G * dim), **f32)
+    kq, beta, decay = torch.empty((T, G), **f32), torch.empty((T, H), **f32), torch.empty((T, H), **f32)
+    lib = build.load("delta_rule")
+    rc = lib.rl_delta_prep(
+        _p(qk), c_int(_dt(qk, "delta_prep")), c_int(_rows(qk, "delta_prep qk")), _p(ba), c_int(_rows(ba, "delta_prep ba")), _p(a_log), _p(dt_bias),
+        c_float(unit_eps), c_float(q_scale), _p(qn), _p(kn), _p(kq), _p(beta), _p(decay), c_int(T), c_int(G), c_int(H), c_int(dim), _stream(),
+    )
+    _check(lib, rc, "delta_prep")
+    return qn, kn, kq, beta, decay
+
+
+def delta_rule(
+    qn: torch.Tensor, kn: torch.Tensor, kq: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+    slot_ids: torch.Tensor, seq_start: torch.Tensor, num_heads: int, num_qk_heads: int, dim: int, vdim: int,
+) -> torch.Tensor:
+    """The gated delta rule through the sequences' states, token by token: S <- g S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q.  qn, kn: float32 [T, G dim]; kq = k . q: float32 [T, G]; v: [T, H vdim] rows of the run's type; beta, decay:
+    float32 [T, H]; state: float32 [slots, H, dim, vdim].  Head h reads q/k head h // (H / G).  Returns float32 [T, H vdim]."""
+    T = qn.shape[0]
+    H, G = num_heads, num_qk_heads
+    for name, t, n in (("qn", qn, G * dim), ("kn", kn, G * dim), ("kq", kq, G), ("beta", beta, H), ("decay", decay, H)):
+        _cuda(t, f"delta_rule {name}", torch.float32)
+        _need(tuple(t.shape) == (T, n), f"delta_rule: {name} {tuple(t.shape)} is not [{T}, {n}]")
+    _cuda(v, "delta_rule v", contiguous=False)
+    _need(tuple(v.shape) == (T, H * vdim), "delta_rule: v must be [T, H vdim]")
+    _need(dim <= DELTA_RULE_MAX_DIM, f"delta_rule: key size {dim} exceeds {DELTA_RULE_MAX_DIM}")
+    _cuda(state, "delta_rule state", torch.float32)
+    _need(state.dim() == 4 and tuple(state.shape[1:]) == (H, dim, vdim), f"delta_rule: state {tuple(state.shape)} is not [slots, {H}, {dim}, {vdim}]")
+    _cuda(slot_ids, "delta_rule slot_ids", torch.int32)
+    _cuda(seq_start, "delta_rule seq_start", torch.int32)
+    S = slot_ids.numel()
+    _need(seq_start.numel() == S + 1, "delta_rule: seq_start must hold one more entry than there are sequences")
+    out = torch.empty((T, H * vdim), dtype=torch.float32, device=qn.device)
+    lib = build.load("delta_rule")
+    rc = lib.rl_delta_rule(
+        _p(qn), _p(kn), _p(kq), _p(v), c_int(_dt(v, "delta_rule v")), c_int(_rows(v, "delta_rule v")), _p(beta), _p(decay), _p(state), _p(slot_ids),
+        _p(seq_start), _p(out), c_int(out.stride(0)), c_int(S), c_int(H), c_int(G), c_int(dim), c_int(vdim), _stream(),
+    )
+    _check(lib, rc, "delta_rule")
+    return out
 
 
 ACT_RELU2 = 1  # relu(x)^2

@@ -1,3 +1,3 @@
 """Architectures.  Importing this package registers them."""
 
-from . import llama, revirax, tefavik, vezatar  # noqa: F401
+from . import llama, namalix, revirax, tefavik, vezatar  # noqa: F401

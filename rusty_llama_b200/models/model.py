@@ -101,6 +101,8 @@ class Model:
     def forward(self, step, cache: Cache, tables: Sequence[torch.Tensor]) -> torch.Tensor:
         """Run the step's tokens through the schedule; float32 logits [len(step.rows), vocab]."""
         stream: ResidualStream = self.embedding.forward(step.tokens)
+        if getattr(step, "shared", None):
+            step.shared.clear()  # (what a run of an earlier step left for its later runs)
         for run, entry in enumerate(self.spec.schedule):
             block = self.blocks[entry.layer]
             if entry.add_input:

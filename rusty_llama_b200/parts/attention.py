@@ -43,7 +43,7 @@ def decode_splits(n_seqs: int, num_heads: int, num_kv_heads: int, kv_len: int, h
 
 _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight", "gate": "g", "sink": "sink", "head_mix": "talk",
           "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias", "q_norm": "q_norm.weight",
-          "k_norm": "k_norm.weight"}
+          "k_norm": "k_norm.weight", "head_bias": "pb", "value_mix": "vmix"}
 
 
 @MIXERS.register("attention")
@@ -65,8 +65,13 @@ class Attention(Mixer):
     of every q and k head over the head's numbers, with one learned weight row for the q heads and one for the k heads, after
     the biases and before the rotation), softcap (0, or the cap c of s <- c tanh(s / c) on the scaled scores), chunk (0, or the
     size of the chunks, counted from position 0, outside of which a query sees nothing; the cache gives back the pages of
-    chunks that are over), names (tensor names after the prefix, keys q k v o gate sink head_mix q_bias k_bias v_bias o_bias
-    q_norm k_norm).
+    chunks that are over), weights ("softmax", or "logistic": no softmax at all; a visible key's weight is logistic(score +
+    head_bias_h), nothing is normalised over the keys, and `head_mix` then mixes the heads' WEIGHTS, after the logistic function),
+    head_bias (bool: one learned number per head, added to the score; with logistic weights only), gate "head" (one gate number
+    per head instead of one per value: Wg is [H, d]), value_mix (None, or {"key": a name, "role": "source" or "mix"}: the
+    "source" layer leaves the values it projected for the step's tokens under that name, a "mix" layer stores and attends to
+    (1 - lambda) v + lambda v_source, lambda a learned number; both kinds of layer have the tensor), names (tensor names after the
+    prefix, keys q k v o gate sink head_mix q_bias k_bias v_bias o_bias q_norm k_norm head_bias value_mix).
     tensors: <prefix>q_proj.weight [H hd, d], k_proj.weight [K hd, d], v_proj.weight [K vd, d],
              o_proj.weight [d, H vd]; with the options also g [H vd, d], sink [H], talk [H, H] and the biases.
              q, k, v (and the gate) are kept as one matrix so that one product
@@ -99,6 +104,17 @@ class Attention(Mixer):
             raise ConfigError(f"attention: softcap {self.softcap} and chunk {self.chunk} must not be negative")
         self.has_mix = bool(spec.params.get("head_mix", False))
         self.has_gate = bool(spec.params.get("gate", False))
+        self.head_gate = spec.params.get("gate") == "head"
+        weights = spec.params.get("weights", "softmax")
+        if weights not in ("softmax", "logistic"):
+            raise ConfigError(f"attention: weights '{weights}' are not built (known: softmax, logistic)")
+        self.logistic = weights == "logistic"
+        self.has_head_bias = bool(spec.params.get("head_bias", False))
+        self.value_mix = spec.params.get("value_mix")
+        if self.value_mix is not None and (self.value_mix.get("role") not in ("source", "mix") or not self.value_mix.get("key")):
+            raise ConfigError("attention: value_mix needs a key and the role 'source' or 'mix'")
+        if (self.has_head_bias or self.head_gate) and not self.logistic:
+            raise ConfigError("attention: a bias per head and a gate per head are built for logistic weights only")
         self.has_bias = bool(spec.params.get("bias", False))
         self.has_o_bias = self.has_bias and spec.params.get("bias") != "qkv"
         self.out_scale = float(spec.params.get("out_scale", 1.0))
@@ -114,6 +130,11 @@ class Attention(Mixer):
         # (the 32-bit attention kernel has none), and in bfloat16 a head size that moves in 16-byte pieces
         plain = self.vd == self.hd and not (self.has_mix or self.has_gate or self.has_bias) and self.out_scale == 1.0 and magnitude == 1.0
         plain = plain and not (self.zero_sink or self.qk_norm_eps is not None or self.softcap or self.chunk)
+        plain = plain and not (self.logistic or self.value_mix is not None)
+        if self.logistic and (self.has_sink or self.zero_sink):
+            raise ConfigError("attention: logistic weights have no denominator for a sink to join")
+        if self.value_mix is not None and self.has_bias:
+            raise ConfigError("attention: value mixing beside biases is not built")
         if plain and self.has_sink:
             plain = runtime.dtype != torch.float32 and self.hd % 8 == 0
         self.extended = not plain
@@ -132,6 +153,8 @@ class Attention(Mixer):
                 f"(a float32 run takes any head size up to 256)")
         self.scale = float(spec.params.get("scale") or 1.0 / math.sqrt(self.hd))
         self.qd, self.kvd, self.vvd, self.od = self.H * self.hd, self.K * self.hd, self.K * self.vd, self.H * self.vd
+        self.gd = self.H if self.head_gate else self.od  # rows of the gate's matrix
+        self.head_bias = self.v_lambda = None
         self.w_qkv = None
         self.w_o = None
         self.b_in = self.b_o = self.sink = self.mix = self.w_q_norm = self.w_k_norm = None
@@ -152,7 +175,11 @@ class Attention(Mixer):
             p + n["o"]: ParamInfo((self.d, self.od)),
         }
         if self.has_gate:
-            infos[p + n["gate"]] = ParamInfo((self.od, self.d))
+            infos[p + n["gate"]] = ParamInfo((self.gd, self.d))
+        if self.has_head_bias:
+            infos[p + n["head_bias"]] = ParamInfo((self.H,), "scalars", centre=0.0)
+        if self.value_mix is not None:
+            infos[p + n["value_mix"]] = ParamInfo((), "scalars", centre=0.5)
         if self.has_sink and not self.zero_sink:
             infos[p + n["sink"]] = ParamInfo((self.H,), "scalars")
         if self.qk_norm_eps is not None:
@@ -181,6 +208,10 @@ class Attention(Mixer):
             self.w_q_norm, self.w_k_norm = tensors[p + n["q_norm"]].contiguous(), tensors[p + n["k_norm"]].contiguous()
         if self.has_mix:
             self.mix = tensors[p + n["head_mix"]].contiguous()
+        if self.has_head_bias:
+            self.head_bias = tensors[p + n["head_bias"]].contiguous()
+        if self.value_mix is not None and self.value_mix["role"] == "mix":
+            self.v_lambda = tensors[p + n["value_mix"]].to(torch.float32).reshape(1).contiguous()
         if self.has_bias:
             self.b_in = torch.cat([tensors[p + n["q_bias"]], tensors[p + n["k_bias"]], tensors[p + n["v_bias"]]]).contiguous()
             if self.has_o_bias:
@@ -198,10 +229,19 @@ class Attention(Mixer):
             raise ConfigError("attention: a layer that reads another layer's cache cannot have this mixer's options")
         proj = linear(xn, self.w_qkv)
         inv_freq, rotary_dim, interleaved, magnitude = self.rotation
+        v_src = None
+        if self.value_mix is not None:
+            key = self.value_mix["key"]
+            if self.value_mix["role"] == "source":  # (its rows are not touched again: the values are stored in the pages as they are)
+                step.shared[key] = proj[:, self.qd + self.kvd : self.qd + self.kvd + self.vvd]
+            else:
+                v_src = step.shared.get(key)
+                if v_src is None or tuple(v_src.shape) != (proj.shape[0], self.vvd):
+                    raise ConfigError(f"attention: no values '{key}' of {self.vvd} numbers a token were left by an earlier layer of this step")
         ops.qkv_prep(
             proj, self.b_in, step.tok_pos, step.tok_seq, cache.block_table, cache.k_pages, cache.v_pages, inv_freq, magnitude,
             self.H, self.K, self.hd, self.vd, rotary_dim, interleaved, q_norm=self.w_q_norm, k_norm=self.w_k_norm,
-            norm_eps=self.qk_norm_eps or 0.0,
+            norm_eps=self.qk_norm_eps or 0.0, v_src=v_src, v_lambda=self.v_lambda if v_src is not None else None,
         )
         gate = proj[:, self.qd + self.kvd + self.vvd :] if self.has_gate else None
         return self._attend(proj, gate, step, cache, out), self.w_o
@@ -212,6 +252,8 @@ class Attention(Mixer):
         128, no mixed scores, no gate), else the tensor-core kernel for unequal sizes, mixed scores and gates; 32-bit runs and
         the remaining sizes take the general kernel."""
         bf = self.rt.dtype == torch.bfloat16
+        if self.logistic:
+            return self._attend_logistic(proj, gate, step, cache, out)
         if (bf and self.hd == self.vd and self.hd in ops.FLASH_TC_HEAD_DIMS and not self.has_mix and gate is None and self.out_scale == 1.0
                 and proj.stride(0) % 8 == 0 and proj.data_ptr() % 16 == 0):
             direct = out is not None and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and out.stride(1) == 1
@@ -266,6 +308,14 @@ class Attention(Mixer):
             proj, cache.k_pages, cache.v_pages, cache.block_table, step.tok_seq, step.tok_pos, self.H, self.K, self.hd, self.vd,
             self.scale, window=self.window, sink=self.sink, mix=self.mix, gate=gate, out_scale=self.out_scale, out=out, chunk=self.chunk,
             softcap=self.softcap,
+        )
+
+    def _attend_logistic(self, proj: torch.Tensor, gate, step, cache, out):
+        """Attention with logistic weights (csrc/attention_sigmoid.cu)."""
+        return ops.sigmoid_attn(
+            proj, cache.k_pages, cache.v_pages, cache.block_table, step.tok_seq, step.tok_pos, self.H, self.K, self.hd, self.vd, self.scale,
+            head_bias=self.head_bias, mix=self.mix, gate=gate, softcap=self.softcap, window=self.window, chunk=self.chunk,
+            out_scale=self.out_scale, out=out,
         )
 
     def forward_unprojected(self, xn: torch.Tensor, step, cache, shared_cache: bool = False, out=None):

@@ -103,3 +103,18 @@ class SandwichBlock(Block):
             return
         xn = self.norms["feed_forward"].forward(stream)
         stream.add(self.feed_forward.forward(xn, step), norm=self.norms["feed_forward_out"].rms_weight())
+
+
+@BLOCKS.register("shared_norm")
+class SharedNormBlock(Block):
+    """x += mixer(norm(x)) + feed_forward(norm(x)): one norm, and both sublayers read its output (the feed-forward may be absent).
+    norms: "mixer".
+
+    The mixer's result and the feed-forward's are two terms of the residual sum; both are 32-bit additions to the stream, the
+    first by a pass of its own when the second is handed over, the second inside the next norm's kernel."""
+
+    def forward(self, stream: ResidualStream, step, cache, shared_cache: bool = False) -> None:
+        xn = self.norms["mixer"].forward(stream)
+        stream.add_result(self.mixer.forward(xn, step, cache, shared_cache), bias=self.mixer.output_bias())
+        if self.feed_forward is not None:
+            stream.add(self.feed_forward.forward(xn, step))

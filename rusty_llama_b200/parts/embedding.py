@@ -13,9 +13,10 @@ from .base import EMBEDDINGS, HEADS, ParamInfo, Part, ResidualStream
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Part):
-    """x = E[token], a row copy without scale (src/model.rs:1237-1242), widened to the 32-bit stream.
+    """x = E[token], a row copy (src/model.rs:1237-1242), widened to the 32-bit stream; times `scale` there if one is named.
 
-    params: vocab_size, hidden_size, name (optional: the tensor's name after the prefix, "weight" if absent).
+    params: vocab_size, hidden_size, name (optional: the tensor's name after the prefix, "weight" if absent), scale (optional,
+    default 1: a constant that the rows are multiplied by, in 32-bit).
     tensor: <prefix>weight [V, d]."""
 
     def __init__(self, spec, runtime):
@@ -23,6 +24,7 @@ class TokenEmbedding(Part):
         self.vocab_size = int(self._param("vocab_size"))
         self.d = int(self._param("hidden_size"))
         self.tensor_name = self.prefix + str(spec.params.get("name", "weight"))
+        self.scale = float(spec.params.get("scale", 1.0))
         self.weight: Optional[torch.Tensor] = None
 
     def param_infos(self) -> Dict[str, ParamInfo]:
@@ -32,7 +34,7 @@ class TokenEmbedding(Part):
         self.weight = tensors[self.tensor_name]
 
     def forward(self, tokens: torch.Tensor) -> ResidualStream:
-        return ResidualStream(ops.embed_gather(tokens, self.weight), self.rt.dtype)
+        return ResidualStream(ops.embed_gather(tokens, self.weight, scale=self.scale), self.rt.dtype)
 
 
 @HEADS.register("linear_head")

@@ -19,9 +19,9 @@ class GatedMLP(FeedForward):
 
     activation "clamped_swish" (params `limit`, `alpha`): f = W_down (g s(alpha g) (u + 1)) with g = min(W_gate x, limit),
     u = clamp(W_up x, -limit, limit), s the logistic function; in bfloat16 the product's kernel applies it as it does silu,
-    in 32-bit a kernel of its own.
+    in 32-bit a kernel of its own.  activation "gelu_tanh": act(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), in the same places.
 
-    params: hidden_size, intermediate_size, activation ("silu" or "clamped_swish"),
+    params: hidden_size, intermediate_size, activation ("silu", "clamped_swish" or "gelu_tanh"),
             names (optional: the three tensors' names after the prefix, keys gate up down).
     tensors: <prefix>gate_proj.weight [ff, d], up_proj.weight [ff, d], down_proj.weight [d, ff].
     gate and up are kept as one [2 ff, d] matrix so that one product serves both, the
@@ -35,10 +35,14 @@ class GatedMLP(FeedForward):
         self.d = int(self._param("hidden_size"))
         self.ff = int(self._param("intermediate_size"))
         self.activation = self._param("activation")
-        if self.activation not in ("silu", "clamped_swish"):
-            raise ConfigError(f"gated_mlp: activation '{self.activation}' is not built (only 'silu' and 'clamped_swish')")
+        if self.activation not in ("silu", "clamped_swish", "gelu_tanh"):
+            raise ConfigError(f"gated_mlp: activation '{self.activation}' is not built (only 'silu', 'clamped_swish' and 'gelu_tanh')")
+        self.act = None  # what the products' kernels are told: None is silu(gate) * up
         if self.activation == "clamped_swish":
             self.limit, self.alpha = float(self._param("limit")), float(self._param("alpha"))
+            self.act = (self.alpha, self.limit)
+        elif self.activation == "gelu_tanh":
+            self.act = "gelu_tanh"
         self.names = dict({"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}, **dict(spec.params.get("names", {})))
         self.w_gate_up = None
         self.w_down = None
@@ -66,9 +70,9 @@ class GatedMLP(FeedForward):
 
     def forward(self, xn: torch.Tensor, step) -> torch.Tensor:
         if self.fused:
-            h = linear_swiglu(xn, self.w_gate_up, act=(self.alpha, self.limit) if self.activation == "clamped_swish" else None)
-        elif self.activation == "clamped_swish":
-            h = ops.clamped_glu(linear(xn, self.w_gate_up), self.alpha, self.limit)
+            h = linear_swiglu(xn, self.w_gate_up, act=self.act)
+        elif self.act is not None:
+            h = ops.gated_glu(linear(xn, self.w_gate_up), self.act)
         else:
             h = ops.swiglu(linear(xn, self.w_gate_up))
         return linear_to_stream(h, self.w_down)

@@ -1,9 +1,9 @@
 """Mixers whose memory is a matrix per head that decays by gates computed from the current token: gated linear attention
-(a decay per key channel) and the matrix memory of xLSTM (mLSTM: scalar input and forget gates per head, kept in range by a
-running maximum).
+(a decay per key channel), the matrix memory of xLSTM (mLSTM: scalar input and forget gates per head, kept in range by a
+running maximum) and the gated delta rule (a decay per head, and a write that corrects what the state already holds for the key).
 
-Both keep their state in 32-bit in the cache's state records, one record per sequence slot, zero when the sequence starts,
-and both run on the same recurrence kernel (csrc/gated_recurrent.cu):
+All keep their state in 32-bit in the cache's state records, one record per sequence slot, zero when the sequence starts;
+the first two run on the same recurrence kernel (csrc/gated_recurrent.cu), the delta rule on its own (csrc/delta_rule.cu):
 
     S_t = diag(a_t) S_(t-1) + b_t k_t v_t^T,   o_t = S_t^T q_t
 
@@ -216,4 +216,99 @@ class MatrixMemory(Mixer):
         a = ops.head_norm_gate(
             o, H, self.vdim, self.w_norm, self.eps, gate, ops.GATE_SIGMOID, xn.dtype, m=m, den_eps=self.den_eps, out_scale=self.out_scale, out=out,
         )
+        return a, self.w_o
+
+
+@MIXERS.register("gated_delta")
+class GatedDeltaRule(Mixer):
+    """The gated delta rule, per head with a state S [dim, vdim]:
+
+        q = act(conv(W_q xn)), k = act(conv(W_k xn))  [G, dim];   v = act(conv(W_v xn))  [H, vdim]     (act = silu)
+        q <- q / sqrt(sum(q^2) + unit_eps) * q_scale,  k <- k / sqrt(sum(k^2) + unit_eps)               (per head)
+        beta = logistic(W_b xn),   g = exp(-exp(A_log) softplus(W_a xn + dt_bias))                      (one number per head each)
+        S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q                                 (head h reads q/k head h // (H / G))
+        result = W_o ( concat_h (o[h] / rms(o[h])) * w_norm * silu(W_g xn) )
+
+    conv is a causal convolution over time per channel with `taps` taps (zeros before a sequence's start); the last taps - 1
+    projected inputs of a sequence are a second record beside S.  Everything after the convolutions' activations is 32-bit.
+
+    params: hidden_size, num_heads, num_qk_heads, dim, vdim, taps, eps (of the heads' norm), unit_eps (default 1e-6),
+            q_scale (default dim^-1/2), out_scale (default 1), names (optional: keys q k v gate norm o b a a_log dt_bias conv).
+    tensors: <prefix>q [G dim, d], k [G dim, d], v [H vdim, d], g [H vdim, d], o [d, H vdim], b [H, d], a [H, d], A_log [H],
+             dt_bias [H], norm [vdim], q.conv [G dim, taps], k.conv [G dim, taps], v.conv [H vdim, taps]."""
+
+    takes_out = True
+    _NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "norm": "norm", "o": "o", "b": "b", "a": "a", "a_log": "A_log", "dt_bias": "dt_bias",
+              "conv": ".conv"}
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.d = int(self._param("hidden_size"))
+        self.H = int(self._param("num_heads"))
+        self.G = int(self._param("num_qk_heads"))
+        self.dim = int(self._param("dim"))
+        self.vdim = int(self._param("vdim"))
+        self.taps = int(self._param("taps"))
+        self.eps = float(self._param("eps"))
+        self.unit_eps = float(spec.params.get("unit_eps", 1e-6))
+        if min(self.H, self.G, self.dim, self.vdim) <= 0 or self.H % self.G or self.dim > ops.DELTA_RULE_MAX_DIM or self.vdim > 512:
+            raise ConfigError(f"gated_delta: sizes heads={self.H} on {self.G} dim={self.dim} vdim={self.vdim} (heads a multiple of the q/k heads, "
+                              f"dim at most {ops.DELTA_RULE_MAX_DIM}, vdim at most 512)")
+        if not 1 <= self.taps <= ops.SHORT_CONV_MAX_TAPS:
+            raise ConfigError(f"gated_delta: {self.taps} taps (1 to {ops.SHORT_CONV_MAX_TAPS})")
+        self.q_scale = float(spec.params.get("q_scale") or self.dim ** -0.5)
+        self.out_scale = float(spec.params.get("out_scale", 1.0))
+        self.names = dict(self._NAMES, **dict(spec.params.get("names", {})))
+        self.qd, self.vd = self.G * self.dim, self.H * self.vdim
+        self.channels = 2 * self.qd + self.vd
+        self.w_in = self.w_conv = self.a_log = self.dt_bias = self.w_o = self.w_norm = None
+
+    def cache_need(self):
+        need = StateNeed((self.H, self.dim, self.vdim), torch.float32)
+        if self.taps > 1:  # the convolutions' last inputs: exact in 32-bit whatever the run's type
+            return (need, StateNeed((self.taps - 1, self.channels), torch.float32))
+        return need
+
+    def param_infos(self) -> Dict[str, ParamInfo]:
+        p, n = self.prefix, self.names
+        return {
+            p + n["q"]: ParamInfo((self.qd, self.d)),
+            p + n["k"]: ParamInfo((self.qd, self.d)),
+            p + n["v"]: ParamInfo((self.vd, self.d)),
+            p + n["gate"]: ParamInfo((self.vd, self.d)),
+            p + n["b"]: ParamInfo((self.H, self.d)),
+            p + n["a"]: ParamInfo((self.H, self.d)),
+            p + n["q"] + n["conv"]: ParamInfo((self.qd, self.taps), "scalars"),
+            p + n["k"] + n["conv"]: ParamInfo((self.qd, self.taps), "scalars"),
+            p + n["v"] + n["conv"]: ParamInfo((self.vd, self.taps), "scalars"),
+            p + n["a_log"]: ParamInfo((self.H,), "scalars", centre=0.0),
+            p + n["dt_bias"]: ParamInfo((self.H,), "scalars", centre=0.0),
+            p + n["norm"]: ParamInfo((self.vdim,), "scalars", centre=1.0),
+            p + n["o"]: ParamInfo((self.d, self.vd)),
+        }
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        p, n = self.prefix, self.names
+        # one product serves q, k, v, the output gate and the two scalars of every head
+        self.w_in = torch.cat([tensors[p + n[key]] for key in ("q", "k", "v", "gate", "b", "a")], dim=0).contiguous()
+        self.w_conv = torch.cat([tensors[p + n[key] + n["conv"]] for key in ("q", "k", "v")], dim=0).contiguous()
+        self.a_log, self.dt_bias = tensors[p + n["a_log"]].contiguous(), tensors[p + n["dt_bias"]].contiguous()
+        self.w_norm = tensors[p + n["norm"]].contiguous()
+        self.w_o = tensors[p + n["o"]].contiguous()
+
+    def forward(self, xn: torch.Tensor, step, cache, shared_cache: bool = False) -> torch.Tensor:
+        a, w_o = self.forward_unprojected(xn, step, cache, shared_cache)
+        return linear_to_stream(a, w_o)
+
+    def forward_unprojected(self, xn: torch.Tensor, step, cache, shared_cache: bool = False, out=None):
+        if shared_cache:
+            raise ConfigError("gated_delta: a state cannot be another run's")
+        memory, inputs = cache if self.taps > 1 else (cache, None)
+        proj = linear(xn, self.w_in)
+        C, vd, H = self.channels, self.vd, self.H
+        conv = ops.short_conv(proj[:, :C], self.w_conv, None if inputs is None else inputs.state, step.slot_ids, step.seq_start, step.tok_seq)
+        gate, ba = proj[:, C : C + vd], proj[:, C + vd : C + vd + 2 * H]
+        qn, kn, kq, beta, decay = ops.delta_prep(conv[:, : 2 * self.qd], ba, self.a_log, self.dt_bias, self.G, H, self.dim, self.unit_eps, self.q_scale)
+        o = ops.delta_rule(qn, kn, kq, conv[:, 2 * self.qd :], beta, decay, memory.state, step.slot_ids, step.seq_start, H, self.G, self.dim, self.vdim)
+        a = ops.head_norm_gate(o, H, self.vdim, self.w_norm, self.eps, gate, ops.GATE_SILU, xn.dtype, out_scale=self.out_scale, out=out)
         return a, self.w_o

@@ -14,7 +14,7 @@ import torch
 from ..errors import ConfigError
 from ..kernels import ops
 from ..kernels.linear import linear, linear_to_stream
-from .base import MIXERS, Mixer, ParamInfo, StateNeed
+from .base import MIXERS, POSITIONS, Mixer, ParamInfo, StateNeed
 
 
 # prompt steps whose longest sequence brings fewer tokens than this go token by token like a decode step
@@ -32,9 +32,16 @@ class DecayLinearAttention(Mixer):
     The norm runs over all heads together.  The recurrence, the norm and the gate are 32-bit; the state [H, dim, vdim] is a
     32-bit record per sequence.
 
+    Options: `position` (a PartSpec of a rotary position encoding: q and k are turned by their positions before the recurrence,
+    v is not), `k_scale` (a constant on k; o is linear in k, so it reaches o as one factor, and since o only ever goes through
+    the norm it is applied there, exactly, as eps / k_scale^2 in the place of eps: the state holds S / k_scale), `head_norm` (every
+    head's o is normed on its own over its vdim values), `norm_weight` (False: the norm has no weight and no tensor), `gate_act`
+    ("sigmoid" or "silu").
+
     params: hidden_size, num_heads, dim, vdim, decay (one number per head), eps (of the norm), activation ("silu" or "none"),
-            gate (bool, default True), out_scale (default 1), names (optional: keys q k v gate norm o).
-    tensors: <prefix>q [H dim, d], k [H dim, d], v [H vdim, d], g [H vdim, d], norm [H vdim], o [d, H vdim]."""
+            gate (bool, default True), out_scale (default 1), position, k_scale, head_norm, norm_weight, gate_act,
+            names (optional: keys q k v gate norm o).
+    tensors: <prefix>q [H dim, d], k [H dim, d], v [H vdim, d], g [H vdim, d], norm [H vdim] ([vdim] with head_norm), o [d, H vdim]."""
 
     takes_out = True
     _NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "norm": "norm", "o": "o"}
@@ -61,9 +68,32 @@ class DecayLinearAttention(Mixer):
         self.names = dict(self._NAMES, **dict(spec.params.get("names", {})))
         self.qd, self.vd = self.H * self.dim, self.H * self.vdim
         self.w_in = self.w_o = self.w_norm = None
+        self.head_norm = bool(spec.params.get("head_norm", False))
+        self.norm_weight = bool(spec.params.get("norm_weight", True))
+        gate_act = spec.params.get("gate_act", "sigmoid")
+        if gate_act not in ("sigmoid", "silu"):
+            raise ConfigError(f"decay_linear_attention: gate_act '{gate_act}' is not built (only 'sigmoid' and 'silu')")
+        self.gate_silu = gate_act == "silu"
+        if (self.gate_silu or not self.norm_weight) and not self.head_norm:
+            raise ConfigError("decay_linear_attention: a silu gate and a norm without weight are built for head_norm only")
+        k_scale = float(spec.params.get("k_scale", 1.0))
+        if not k_scale > 0:
+            raise ConfigError(f"decay_linear_attention: k_scale = {k_scale} must be positive")
+        self.norm_eps = self.eps / (k_scale * k_scale)
+        self.position = None
+        pos_spec = spec.params.get("position")
+        if pos_spec is not None and pos_spec.kind != "none":
+            self.position = POSITIONS.build(pos_spec, runtime)
+            if not hasattr(self.position, "inv_freq") or float(getattr(self.position, "magnitude", 1.0)) != 1.0:
+                raise ConfigError("decay_linear_attention: the position part must be a 'rotary' one without a magnitude factor")
+            if int(self.position.rotary_dim) > self.dim:
+                raise ConfigError(f"decay_linear_attention: {self.position.rotary_dim} rotated numbers do not fit a head of {self.dim}")
 
     def cache_need(self):
         return StateNeed((self.H, self.dim, self.vdim), torch.float32)
+
+    def children(self):
+        return () if self.position is None else (self.position,)
 
     def param_infos(self) -> Dict[str, ParamInfo]:
         p, n = self.prefix, self.names
@@ -71,9 +101,10 @@ class DecayLinearAttention(Mixer):
             p + n["q"]: ParamInfo((self.qd, self.d)),
             p + n["k"]: ParamInfo((self.qd, self.d)),
             p + n["v"]: ParamInfo((self.vd, self.d)),
-            p + n["norm"]: ParamInfo((self.vd,), "scalars", centre=1.0),
             p + n["o"]: ParamInfo((self.d, self.vd)),
         }
+        if self.norm_weight:
+            infos[p + n["norm"]] = ParamInfo((self.vdim if self.head_norm else self.vd,), "scalars", centre=1.0)
         if self.has_gate:
             infos[p + n["gate"]] = ParamInfo((self.vd, self.d))
         return infos
@@ -84,7 +115,7 @@ class DecayLinearAttention(Mixer):
         if self.has_gate:
             parts.append(tensors[p + n["gate"]])
         self.w_in = torch.cat(parts, dim=0).contiguous()  # one product serves q, k, v and the gate
-        self.w_norm = tensors[p + n["norm"]].contiguous()
+        self.w_norm = tensors[p + n["norm"]].contiguous() if self.norm_weight else None
         self.w_o = tensors[p + n["o"]].contiguous()
 
     def forward(self, xn: torch.Tensor, step, cache, shared_cache: bool = False) -> torch.Tensor:
@@ -95,6 +126,10 @@ class DecayLinearAttention(Mixer):
         if shared_cache:
             raise ConfigError("decay_linear_attention: a state cannot be another run's")
         proj = linear(xn, self.w_in)
+        if self.position is not None and self.position.rotary_dim:
+            # q and k lie side by side at the start of the rows: 2 H heads turned in place, nothing stored anywhere else
+            ops.rope_kv_write(proj, step.tok_pos, step.tok_seq, None, None, None, self.position.inv_freq, 2 * self.H, 0, self.dim,
+                              self.position.rotary_dim, self.position.interleaved, write_kv=False)
         q, k = proj[:, : self.qd], proj[:, self.qd : 2 * self.qd]
         v = proj[:, 2 * self.qd : 2 * self.qd + self.vd]
         gate = proj[:, 2 * self.qd + self.vd :] if self.has_gate else None
@@ -109,7 +144,11 @@ class DecayLinearAttention(Mixer):
             q, k, v, self.decay, cache.state, step.slot_ids, step.seq_start, self.H, self.dim, self.vdim, silu=self.silu,
             max_q_len=step.max_q_len if chunked else 0, scratch=scratch,
         )
-        a = ops.rms_gate(o, self.w_norm, self.eps, gate, xn.dtype, out_scale=self.out_scale, out=out)
+        if self.head_norm:
+            a = ops.head_norm_gate(o, self.H, self.vdim, self.w_norm, self.norm_eps, gate, ops.GATE_SILU if self.gate_silu else ops.GATE_SIGMOID,
+                                   xn.dtype, out_scale=self.out_scale, out=out)
+        else:
+            a = ops.rms_gate(o, self.w_norm, self.norm_eps, gate, xn.dtype, out_scale=self.out_scale, out=out)
         return a, self.w_o
 
 

@@ -26,6 +26,9 @@ class RoutedExperts(FeedForward):
         y = sum over chosen e of s_e f_e(x)            (s_e / sum of the chosen s if `renormalize`)
           + sigmoid(w_sg . x) * f_shared(x)            (if there is a shared expert; without w_sg it is added as it is)
 
+    router "sigmoid": s = logistic(W_r x), every expert's score on its own; `renorm_eps` joins the sum that `renormalize` divides
+    by, and `weight_scale` multiplies the weights (both also with the softmax router; defaults 0 and 1).
+
     router "table" instead: no scores at all; a table [vocab, top] of expert ids gives every token id its experts (the entries
     of a row differ), and each chosen expert has the weight 1 / top.
 
@@ -33,7 +36,8 @@ class RoutedExperts(FeedForward):
     u = clamp(W_up[e] x, -limit, limit), s the logistic function, in the place of silu(g) * u.
 
     params: hidden_size, n_experts, top, expert_ff, bias (bool), renormalize (bool),
-            shared_ff (0: none), shared_gate (bool), router ("softmax" or "table"; with "table" also vocab_size), activation
+            shared_ff (0: none), shared_gate (bool), router ("softmax", "sigmoid" or "table"; with "table" also vocab_size), renorm_eps,
+            weight_scale, activation
             ("silu" or "clamped_swish"), names (optional).
     tensors: <prefix>e<i>.gate [ff, d], e<i>.up [ff, d], e<i>.down [d, ff], router [E, d] (or table [vocab, top]), correction [E],
              shared.gate / shared.up / shared.down, shared.sg [1, d]."""
@@ -50,8 +54,10 @@ class RoutedExperts(FeedForward):
         self.shared_gate = bool(spec.params.get("shared_gate", False)) and self.shared_ff > 0
         self.names = dict(_NAMES, **dict(spec.params.get("names", {})))
         self.router = spec.params.get("router", "softmax")
-        if self.router not in ("softmax", "table"):
-            raise ConfigError(f"routed_experts: router '{self.router}' is not built (known: softmax, table)")
+        if self.router not in ("softmax", "sigmoid", "table"):
+            raise ConfigError(f"routed_experts: router '{self.router}' is not built (known: softmax, sigmoid, table)")
+        self.renorm_eps = float(spec.params.get("renorm_eps", 0.0))
+        self.weight_scale = float(spec.params.get("weight_scale", 1.0))
         if self.router == "table":
             self.vocab = int(self._param("vocab_size"))
             if self.has_bias or self.renormalize or self.shared_gate:
@@ -119,7 +125,8 @@ class RoutedExperts(FeedForward):
             ids, weights = ops.moe_table_lookup(step.tokens, self.table, self.E)
             gate = None
         else:
-            ids, weights, gate = ops.moe_router(xn, self.w_router, self.bias, self.E, self.top, self.renormalize)
+            ids, weights, gate = ops.moe_router(xn, self.w_router, self.bias, self.E, self.top, self.renormalize,
+                                                logistic=self.router == "sigmoid", renorm_eps=self.renorm_eps, weight_scale=self.weight_scale)
         # the height of a row tile: 128 once the experts get that many rows on average (a prompt step), else 32; the plain
         # kernels of a 32-bit run have their own
         tile_rows = 0
