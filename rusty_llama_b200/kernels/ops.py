@@ -512,6 +512,9 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = Non
     return out
 
 
+GATED_ACTS = ("gelu_tanh",)  # activations of a gate/up product that are named by a string (a pair (alpha, limit) names the clamped form)
+
+
 def _act(act):
     """(alpha, limit) of a gate/up product's activation as the launchers take it: None is silu(gate) * up.
     "relu2": the code with which a product that is NOT a gate/up product sends its sums through relu(x)^2."""
@@ -660,7 +663,9 @@ def gemv_stream(
     _need(w.shape[1] == K, f"gemv_stream: x[{M}, {K}] against w[{N}, {w.shape[1]}]")
     n_out = N // 2 if swiglu else N
     used = c_int(1)
-    _need(not isinstance(act, str) or (not swiglu and k_splits == 1 and row_scale is None), "gemv_stream: an activation of one argument goes with a plain product and whole sums")
+    _need(act in GATED_ACTS or not isinstance(act, str) or (not swiglu and k_splits == 1 and row_scale is None),
+          "gemv_stream: an activation of one argument goes with a plain product and whole sums")
+    _need(act not in GATED_ACTS or swiglu, "gemv_stream: a gate's activation goes with a gate/up product")
     slices = max(1, gemv_stream_slices(M, K, k_splits))  # (0: the launcher says what it does not take)
     _need(k_splits > 1 or slices == 1, f"gemv_stream: k = {K} comes in {slices} slices, whose float32 partial sums have to be asked for (k_splits > 1)")
     if k_splits > 1 and slices > 1:
