@@ -165,8 +165,10 @@ def _layer(i: int, d: Mapping[str, Any]) -> NamalixLayerConfig:
             raise ConfigError(f"{w}: {heads} heads are not a multiple of {kv_heads} kv_heads")
         mixer = AttentionMixerConfig(
             heads=heads, kv_heads=kv_heads, dim=dim, vdim=_int(m, "vdim", w), scale=_num(m, "scale", w),
-            softcap=_num(m, "softcap", w) if m.get("softcap") is not None else 0.0, v_mix=bool(m.get("v_mix", False)), rot=_rotation(m, w, dim),
+            softcap=_num(m, "softcap", w, positive=False) if m.get("softcap") is not None else 0.0, v_mix=bool(m.get("v_mix", False)), rot=_rotation(m, w, dim),
         )
+        if mixer.softcap < 0:
+            raise ConfigError(f"{w}.softcap = {mixer.softcap} must not be negative (0: no cap)")
     elif kind == "retention":
         heads, dim = _int(m, "heads", w), _int(m, "dim", w)
         decay = _get(m, "decay", w)

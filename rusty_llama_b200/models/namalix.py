@@ -106,6 +106,8 @@ def describe_namalix(cfg: NamalixConfig) -> ModelSpec:
         final_norm=norm("final.norm"),
         head=PartSpec("linear_head", {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "tied_to": None, "name": ""}, "head"),
         stored_dtype="bfloat16",
+        # (a checkpoint may carry the mixing factor also in attention layers that mix no values)
+        redundant_tensors=("l*.mix." + _ATTENTION_NAMES["value_mix"],),
     )
 
 

@@ -404,3 +404,28 @@ def chunked_attention_runner(proj, k_pages, v_pages, block_table, step, num_head
     )
     cache = SimpleNamespace(k_pages=k_pages, v_pages=v_pages, block_table=block_table)
     return lambda: Attention._attend(part, proj, None, step, cache, None)
+
+
+def logistic_attention_runner(proj, gate, k_pages, v_pages, block_table, step, num_heads: int, num_kv_heads: int, kdim: int, vdim: int, scale: float,
+                              softcap: float, head_bias, mix, window: int = 0, chunk: int = 0, workspace=None):
+    """A callable that runs the attention with logistic weights as `Attention` does (the kernel choice included) over ready rows,
+    for testing and timing it alone.  gate: [T, >= H] rows or None.  step: tok_seq, tok_pos, seq_start, seq_pos0, max_q_len, n_seqs,
+    decode_only, plan_kv_len."""
+    from types import SimpleNamespace
+
+    class _Scratch:
+        def __init__(self):
+            self.held = {}
+
+        def get(self, name, numel, dtype, zeroed=False):
+            buf = self.held.get(name)
+            if buf is None or buf.numel() < numel or buf.dtype != dtype:
+                buf = self.held[name] = torch.zeros(int(numel), dtype=dtype, device=proj.device)
+            return buf
+
+    part = SimpleNamespace(
+        rt=SimpleNamespace(dtype=proj.dtype, workspace=workspace or _Scratch()), H=num_heads, K=num_kv_heads, hd=kdim, vd=vdim, scale=scale,
+        window=window, chunk=chunk, softcap=softcap, head_bias=head_bias, mix=mix, out_scale=1.0,
+    )
+    cache = SimpleNamespace(k_pages=k_pages, v_pages=v_pages, block_table=block_table)
+    return lambda: Attention._attend_logistic(part, proj, gate, step, cache, None)
