@@ -13,7 +13,8 @@
 //                     head; beta = logistic(b); g = exp(-exp(A_log) softplus(a + dt_bias)): all 32-bit, written as float32
 //   delta_rule        the recurrence, token by token: a block owns 32 columns of one head's state of one sequence, a
 //                     thread 32 rows of one column in registers; a column's state evolves on its own, so the blocks never
-//                     meet; the partial sums of a column's row slices are added in a fixed order.  Prompts, parts of
+//                     meet; the partial sums of a column's row slices (lanes of one warp) are added by shuffles in a fixed
+//                     order, and u_t is folded into the read-out: o_t = (g S)^T q + u (k . q).  Prompts, parts of
 //                     prompts and single tokens run the same code, so a result's bits depend neither on how a sequence
 //                     was cut into steps nor on what else is in the batch.
 #include "common.cuh"
@@ -151,12 +152,17 @@ RL_API int rl_delta_prep(const void* qk, int dtype, int qk_stride, const void* b
 }
 
 // ---------------------------------------------------------------- the recurrence
-#define DR_COLS 32   // columns of the state a block owns
-#define DR_ROWS 32   // rows of a column a thread holds
-#define DR_TOKENS 8  // tokens whose q, k and scalars are staged in shared memory at a time
+#define DR_COLS 32    // columns of the state a block owns
+#define DR_ROWS 32    // rows of a column a thread holds
+#define DR_TOKENS 16  // tokens whose q, k and scalars are staged in shared memory at a time
 #define DR_MAX_SLICES 8
+// q and k of a staged token lie in shared memory with four floats of padding after every 32, so that the threads of a column,
+// who read the same place of different row slices, read different banks, sixteen bytes a load
+#define DR_SKEW(d) ((d) + (((d) >> 5) << 2))
 
-// grid (column tiles, H, sequences); block (DR_COLS, P) with P = ceil(dim / DR_ROWS) row slices.
+// grid (column tiles, H, sequences); block DR_COLS * P threads, P = the row slices of 32 (a power of two): thread
+// col * P + slice holds rows 32 slice .. of one column, so a column's slices are neighbouring lanes of one warp and their partial
+// sums meet by shuffles, in a fixed order; the block meets only where the next tokens are staged.
 // qn, kn: float32 [T, G dim]; kq: [T, G]; v: [T, >= H vdim] rows of T; beta, decay: float32 [T, H];
 // state: float32 [slots, H, dim, vdim]; out: float32 [T, H vdim].
 template <typename T>
@@ -164,30 +170,32 @@ __global__ void __launch_bounds__(DR_COLS * DR_MAX_SLICES)
 delta_rule_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ kq, const T* __restrict__ v,
                   int v_stride, const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
                   const int* __restrict__ slot_ids, const int* __restrict__ seq_start, float* __restrict__ out, int out_stride, int H, int G,
-                  int dim, int vdim) {
-  extern __shared__ float sm[];  // q [DR_TOKENS][dim], k [DR_TOKENS][dim], partial [P][DR_COLS][2]
+                  int dim, int vdim, int P) {
+  extern __shared__ __align__(16) float sm[];  // q [DR_TOKENS][skewed dim], k [DR_TOKENS][skewed dim]
   __shared__ float sc_beta[DR_TOKENS], sc_decay[DR_TOKENS], sc_kq[DR_TOKENS];
-  const int col_l = threadIdx.x, slice = threadIdx.y, P = blockDim.y;
-  const int tid = slice * DR_COLS + col_l, nthreads = DR_COLS * P;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int col_l = tid / P, slice = tid - col_l * P;
   const int h = blockIdx.y, s = blockIdx.z, kh = h / (H / G);
   const int col = blockIdx.x * DR_COLS + col_l;
   const bool col_ok = col < vdim;
   const int row0 = slice * DR_ROWS;
+  const int sdim = DR_SKEW(P * DR_ROWS);  // a staged row's length
   float* q_s = sm;
-  float* k_s = sm + (size_t)DR_TOKENS * dim;
-  float* part = k_s + (size_t)DR_TOKENS * dim;
+  float* k_s = sm + (size_t)DR_TOKENS * sdim;
   float* S_g = state + (((size_t)slot_ids[s] * H + h) * dim) * vdim;
   float S[DR_ROWS];
 #pragma unroll
   for (int r = 0; r < DR_ROWS; ++r) S[r] = (col_ok && row0 + r < dim) ? S_g[(size_t)(row0 + r) * vdim + col] : 0.f;
   const int t0 = seq_start[s], t1 = seq_start[s + 1];
+  const int padded = P * DR_ROWS;
   for (int tb = t0; tb < t1; tb += DR_TOKENS) {
     const int nt = min(DR_TOKENS, t1 - tb);
     __syncthreads();  // the tokens staged before have been used
-    for (int i = tid; i < nt * dim; i += nthreads) {
-      const int j = i / dim, d = i - j * dim;
-      q_s[j * dim + d] = qn[((size_t)(tb + j) * G + kh) * dim + d];
-      k_s[j * dim + d] = kn[((size_t)(tb + j) * G + kh) * dim + d];
+    for (int i = tid; i < nt * padded; i += nthreads) {
+      const int j = i / padded, d = i - j * padded;
+      const bool in = d < dim;  // (rows past the key size read zeros: their state is zero and stays so)
+      q_s[j * sdim + DR_SKEW(d)] = in ? qn[((size_t)(tb + j) * G + kh) * dim + d] : 0.f;
+      k_s[j * sdim + DR_SKEW(d)] = in ? kn[((size_t)(tb + j) * G + kh) * dim + d] : 0.f;
     }
     if (tid < nt) {
       sc_beta[tid] = beta[(size_t)(tb + tid) * H + h];
@@ -195,36 +203,36 @@ delta_rule_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
       sc_kq[tid] = kq[(size_t)(tb + tid) * G + kh];
     }
     __syncthreads();
+    float v_next = (col_ok && slice == 0) ? to_f32(v[(size_t)tb * v_stride + (size_t)h * vdim + col]) : 0.f;
     for (int j = 0; j < nt; ++j) {
       const float g = sc_decay[j];
-      const float* kj = k_s + j * dim + row0;
-      const float* qj = q_s + j * dim + row0;
+      const float4* kj = reinterpret_cast<const float4*>(k_s + j * sdim + DR_SKEW(row0));
+      const float4* qj = reinterpret_cast<const float4*>(q_s + j * sdim + DR_SKEW(row0));
+      const float vj = v_next;
+      if (j + 1 < nt && col_ok && slice == 0) v_next = to_f32(v[(size_t)(tb + j + 1) * v_stride + (size_t)h * vdim + col]);
+      float kr[DR_ROWS];
       float a = 0.f, b = 0.f;
 #pragma unroll
-      for (int r = 0; r < DR_ROWS; ++r) {
-        if (row0 + r < dim) {
-          S[r] *= g;
-          a += S[r] * kj[r];
-          b += S[r] * qj[r];
-        }
-      }
-      if (P > 1) {
-        part[(slice * DR_COLS + col_l) * 2] = a;
-        part[(slice * DR_COLS + col_l) * 2 + 1] = b;
-        __syncthreads();
-        a = 0.f;
-        b = 0.f;
-        for (int p = 0; p < P; ++p) {
-          a += part[(p * DR_COLS + col_l) * 2];
-          b += part[(p * DR_COLS + col_l) * 2 + 1];
-        }
-        __syncthreads();  // (before the next token's partial sums are written)
-      }
-      const float vj = col_ok ? to_f32(v[(size_t)(tb + j) * v_stride + (size_t)h * vdim + col]) : 0.f;
-      const float u = sc_beta[j] * (vj - a);
+      for (int r4 = 0; r4 < DR_ROWS / 4; ++r4) {
+        const float4 k4 = kj[r4], q4 = qj[r4];
+        kr[4 * r4] = k4.x; kr[4 * r4 + 1] = k4.y; kr[4 * r4 + 2] = k4.z; kr[4 * r4 + 3] = k4.w;
+        const float qr[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-      for (int r = 0; r < DR_ROWS; ++r)
-        if (row0 + r < dim) S[r] += kj[r] * u;
+        for (int e = 0; e < 4; ++e) {
+          const int r = 4 * r4 + e;
+          S[r] *= g;
+          a += S[r] * kr[r];
+          b += S[r] * qr[e];
+        }
+      }
+      for (int o = 1; o < P; o <<= 1) {  // the slices of a column are neighbouring lanes; every lane ends with the same sums
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        b += __shfl_xor_sync(0xffffffffu, b, o);
+      }
+      const float vv = __shfl_sync(0xffffffffu, vj, (tid & 31) - slice);  // the column's value, read by its first slice
+      const float u = sc_beta[j] * (vv - a);
+#pragma unroll
+      for (int r = 0; r < DR_ROWS; ++r) S[r] += kr[r] * u;
       if (slice == 0 && col_ok) out[(size_t)(tb + j) * out_stride + (size_t)h * vdim + col] = b + u * sc_kq[j];
     }
   }
@@ -238,18 +246,19 @@ RL_API int rl_delta_rule(const float* qn, const float* kn, const float* kq, cons
                          int H, int G, int dim, int vdim, cudaStream_t stream) {
   if (n_seqs <= 0 || H <= 0 || G <= 0 || dim <= 0 || vdim <= 0) RL_REFUSE(1, "delta_rule: S=%d H=%d G=%d dim=%d vdim=%d", n_seqs, H, G, dim, vdim);
   if (H % G) RL_REFUSE(2, "delta_rule: %d heads are not a multiple of %d q/k heads", H, G);
-  const int P = (dim + DR_ROWS - 1) / DR_ROWS;
+  int P = 1;
+  while (P * DR_ROWS < dim) P <<= 1;
   if (P > DR_MAX_SLICES) RL_REFUSE(3, "delta_rule: key size %d exceeds %d", dim, DR_ROWS * DR_MAX_SLICES);
   if (H > 65535 || n_seqs > 65535) RL_REFUSE(4, "delta_rule: %d heads or %d sequences exceed the grid", H, n_seqs);
   if (v_stride < H * vdim || out_stride < H * vdim) RL_REFUSE(5, "delta_rule: rows shorter than %d values", H * vdim);
-  dim3 grid((vdim + DR_COLS - 1) / DR_COLS, H, n_seqs), block(DR_COLS, P);
-  const size_t smem = ((size_t)2 * DR_TOKENS * dim + (size_t)P * DR_COLS * 2) * sizeof(float);
+  dim3 grid((vdim + DR_COLS - 1) / DR_COLS, H, n_seqs), block(DR_COLS * P);
+  const size_t smem = (size_t)2 * DR_TOKENS * DR_SKEW(P * DR_ROWS) * sizeof(float);
   if (dtype == RL_BF16)
     delta_rule_kernel<bf16><<<grid, block, smem, stream>>>(qn, kn, kq, (const bf16*)v, v_stride, beta, decay, state, slot_ids, seq_start, out,
-                                                           out_stride, H, G, dim, vdim);
+                                                           out_stride, H, G, dim, vdim, P);
   else if (dtype == RL_F32)
     delta_rule_kernel<float><<<grid, block, smem, stream>>>(qn, kn, kq, (const float*)v, v_stride, beta, decay, state, slot_ids, seq_start, out,
-                                                            out_stride, H, G, dim, vdim);
+                                                            out_stride, H, G, dim, vdim, P);
   else
     RL_REFUSE(6, "delta_rule: unknown dtype %d", dtype);
   RL_LAUNCH_RESULT();

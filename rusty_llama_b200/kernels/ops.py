@@ -1435,6 +1435,64 @@ def sigmoid_attn(
     return out
 
 
+def sigmoid_attn_mma_takes(kdim: int, vdim: int, num_heads: int) -> bool:
+    """Whether the tensor-core form of the attention with logistic weights is built for these sizes (bfloat16 only)."""
+    return kdim % 8 == 0 and vdim % 8 == 0 and 0 < kdim <= 128 and 0 < vdim <= 128 and num_heads * vdim * 4 <= 48 * 1024
+
+
+def sigmoid_attn_mma_scratch_floats(n_tokens: int, num_heads: int, num_kv_heads: int, vdim: int, mixed: bool, parts: int) -> int:
+    return parts * n_tokens * num_heads * (num_kv_heads if mixed else 1) * vdim
+
+
+def sigmoid_attn_mma(
+    q: torch.Tensor, k_pages, v_pages, block_table, seq_start, seq_pos0, max_q_len: int, num_heads: int, num_kv_heads: int, kdim: int, vdim: int,
+    scale: float, scratch: torch.Tensor, parts: int = 1, head_bias: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+    gate: Optional[torch.Tensor] = None, softcap: float = 0.0, window: int = 0, chunk: int = 0, out_scale: float = 1.0,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """`sigmoid_attn` on the tensor cores, bfloat16, key and value sizes in multiples of 8 up to 128: the sequences' query rows
+    (tokens seq_start[i] .. seq_start[i+1] at positions seq_pos0[i] ..) against their cached keys.  parts: into how many runs
+    of pages a block's key range is cut (more blocks for a decode step; the partial sums add up in the second kernel).
+    scratch: float32, `sigmoid_attn_mma_scratch_floats(...)` numbers."""
+    _cuda(q, "sigmoid_attn_mma q", torch.bfloat16, contiguous=False)
+    qs = _rows(q, "sigmoid_attn_mma q")
+    T = q.shape[0]
+    _need(q.shape[1] >= num_heads * kdim, "sigmoid_attn_mma: q rows too short")
+    _need(sigmoid_attn_mma_takes(kdim, vdim, num_heads), f"sigmoid_attn_mma: sizes {kdim}, {vdim} with {num_heads} heads are not built")
+    _check_kv_pages(k_pages, v_pages, q.dtype, num_kv_heads, kdim, vdim, "sigmoid_attn_mma")
+    _cuda(block_table, "sigmoid_attn_mma block_table", torch.int32)
+    _cuda(seq_start, "sigmoid_attn_mma seq_start", torch.int32)
+    _cuda(seq_pos0, "sigmoid_attn_mma seq_pos0", torch.int32)
+    S = seq_pos0.numel()
+    _need(seq_start.numel() == S + 1 and block_table.dim() == 2 and block_table.shape[0] == S, "sigmoid_attn_mma: metadata sizes")
+    if head_bias is not None:
+        _cuda(head_bias, "sigmoid_attn_mma head_bias", torch.float32)
+        _need(head_bias.numel() == num_heads, "sigmoid_attn_mma: one bias per head")
+    if mix is not None:
+        _cuda(mix, "sigmoid_attn_mma mix", torch.float32)
+        _need(tuple(mix.shape) == (num_heads, num_heads), "sigmoid_attn_mma: the mixing matrix must be [H, H]")
+    gs = 0
+    if gate is not None:
+        _cuda(gate, "sigmoid_attn_mma gate", q.dtype, contiguous=False)
+        gs = _rows(gate, "sigmoid_attn_mma gate")
+        _need(gate.shape[0] == T and gate.shape[1] >= num_heads, "sigmoid_attn_mma: gate rows too short")
+    _cuda(scratch, "sigmoid_attn_mma scratch", torch.float32)
+    _need(parts >= 1 and scratch.numel() >= sigmoid_attn_mma_scratch_floats(T, num_heads, num_kv_heads, vdim, mix is not None, parts),
+          "sigmoid_attn_mma: scratch too small")
+    if out is None:
+        out = torch.empty((T, num_heads * vdim), dtype=q.dtype, device=q.device)
+    _cuda(out, "sigmoid_attn_mma out", q.dtype, contiguous=False)
+    _need(_rows(out, "sigmoid_attn_mma out") >= num_heads * vdim and tuple(out.shape) == (T, num_heads * vdim), "sigmoid_attn_mma: out must be [T, H vdim]")
+    lib = build.load("attention_sigmoid")
+    rc = lib.rl_sigmoid_attn_mma(
+        _p(q), c_ll(qs), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]), _p(seq_start), _p(seq_pos0), _p(head_bias), _p(mix),
+        _p(gate), c_int(gs), c_float(out_scale), _p(scratch), c_int(parts), _p(out), c_int(out.stride(0)), c_int(T), c_int(S), c_int(max_q_len),
+        c_int(num_heads), c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(window), c_float(scale), c_int(chunk), c_float(softcap), _stream(),
+    )
+    _check(lib, rc, "sigmoid_attn_mma", kernels=2)
+    return out
+
+
 # ------------------------------------------------------------------ recurrent mixers (csrc/recurrent.cu)
 DECAY_CHUNK = 64  # tokens per chunk of the chunked kernels
 DECAY_CHUNKED_MAX_DIM = 256

@@ -311,7 +311,25 @@ class Attention(Mixer):
         )
 
     def _attend_logistic(self, proj: torch.Tensor, gate, step, cache, out):
-        """Attention with logistic weights (csrc/attention_sigmoid.cu)."""
+        """Attention with logistic weights (csrc/attention_sigmoid.cu): bfloat16 runs at key and value sizes in multiples of 8 up to
+        128 on the tensor cores (a decode step's key range cut into runs of pages so that the blocks fill the GPU), everything
+        else on the general kernel, whose sums have one fixed order."""
+        if (self.rt.dtype == torch.bfloat16 and ops.sigmoid_attn_mma_takes(self.hd, self.vd, self.H) and proj.stride(0) % 8 == 0
+                and proj.data_ptr() % 16 == 0):
+            T, mixed = proj.shape[0], self.mix is not None
+            parts = 1
+            if step.decode_only:
+                keys = min(self.window, step.plan_kv_len) if self.window else step.plan_kv_len
+                keys = min(self.chunk, keys) if self.chunk else keys
+                pages = (keys + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE + (1 if (self.window or self.chunk) else 0)
+                blocks = step.n_seqs * self.H * (self.K if mixed else 1)
+                parts = max(1, min(4 * sm_count(proj.device) // max(blocks, 1), pages, 64))
+            scratch = self.rt.workspace.get("sigmoid_attn_parts", ops.sigmoid_attn_mma_scratch_floats(T, self.H, self.K, self.vd, mixed, parts), torch.float32)
+            return ops.sigmoid_attn_mma(
+                proj, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0, step.max_q_len, self.H, self.K, self.hd,
+                self.vd, self.scale, scratch, parts=parts, head_bias=self.head_bias, mix=self.mix, gate=gate, softcap=self.softcap,
+                window=self.window, chunk=self.chunk, out_scale=self.out_scale, out=out,
+            )
         return ops.sigmoid_attn(
             proj, cache.k_pages, cache.v_pages, cache.block_table, step.tok_seq, step.tok_pos, self.H, self.K, self.hd, self.vd, self.scale,
             head_bias=self.head_bias, mix=self.mix, gate=gate, softcap=self.softcap, window=self.window, chunk=self.chunk,
@@ -399,7 +417,7 @@ def chunked_attention_runner(proj, k_pages, v_pages, block_table, step, num_head
         step.plan_kv_len = int(step.seq_len.max())
     part = SimpleNamespace(
         rt=SimpleNamespace(dtype=proj.dtype, workspace=workspace or _Scratch()), H=num_heads, K=num_kv_heads, hd=kdim, vd=vdim, scale=scale,
-        window=window, chunk=chunk, softcap=softcap, sink=sink, mix=None, has_mix=False, out_scale=1.0, fold_matrix=None,
+        window=window, chunk=chunk, softcap=softcap, sink=sink, mix=None, has_mix=False, out_scale=1.0, fold_matrix=None, logistic=False,
         qd=num_heads * kdim, kvd=num_kv_heads * kdim, vvd=num_kv_heads * vdim,
     )
     cache = SimpleNamespace(k_pages=k_pages, v_pages=v_pages, block_table=block_table)
