@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--reps R]
     python bench.py --sizes 1b|13b --workload
-    python bench.py --design vezatar|revirax|tefavik [--design-sizes small,lite,wide]
+    python bench.py --design vezatar|revirax|tefavik|namalix [--design-sizes small,lite,wide]
 
 The default run has the layer sizes of Llama-3.1-8B (BASELINE.json configs[2]) with random
 bfloat16 weights, a batch of 8 sequences and a context of 4096.  A step is one decode step of the
@@ -474,7 +474,7 @@ def main() -> int:
     ap.add_argument("--reps", type=int, default=5, help="repetitions of the timed steps (mean and standard deviation are reported)")
     ap.add_argument("--no-kernels", action="store_true", help="leave out the kernel-by-kernel table")
     ap.add_argument("--workload", action="store_true", help="with --sizes 1b or 13b: BASELINE.json's workload of unequal prompts through LLM.generate, instead of the contract line")
-    ap.add_argument("--design", default="", choices=["", "vezatar", "revirax", "tefavik"], help="instead of the contract line: this design beside Llama (Tefavik: beside Revirax) at equal sizes (prompt and decode steps through the engine, and its kernels alone)")
+    ap.add_argument("--design", default="", choices=["", "vezatar", "revirax", "tefavik", "namalix"], help="instead of the contract line: this design beside Llama (Tefavik and Namalix: beside Revirax) at equal sizes (prompt and decode steps through the engine, and its kernels alone)")
     ap.add_argument("--design-sizes", default="small,lite", help="with --design: which of the sizes small, lite, wide")
     ap.add_argument("--design-tokens", type=int, default=2048, help="with --design: tokens of the prompt step, and the context of the decode steps")
     args = ap.parse_args()
@@ -483,6 +483,8 @@ def main() -> int:
             from rusty_llama_b200.kernels import revirax_bench as design_bench
         elif args.design == "tefavik":
             from rusty_llama_b200.kernels import tefavik_bench as design_bench
+        elif args.design == "namalix":
+            from rusty_llama_b200.kernels import namalix_bench as design_bench
         else:
             from rusty_llama_b200.kernels import design_bench
 

@@ -23,7 +23,8 @@
 //
 //     o_h = sum_g M[h][g] P[g][kv(h)],       P[g][c] = sum_j w_g(i, j) v_c(j)
 //
-// A block takes 64 queries of one sequence (16 in a decode step), ONE query head g and ONE kv head c of values: S = Q_g
+// A block takes 64 queries of one sequence, ONE query head g and ONE kv head c of values (in a decode step, where every
+// sequence brings one token: the heads of one kv head as its rows, so that their keys are read once): S = Q_g
 // K_kv(g)^T per key tile of one page as in any flash kernel, the weights from the 32-bit scores in registers (no running
 // maximum, no rescaling: the sum over the keys is a plain sum), rounded to bfloat16 for the product with V_c, P[g][c] in
 // 32-bit registers.  With a mixing matrix the grid has a block for every c, without one only for c = kv(g).  P goes to a
@@ -178,7 +179,9 @@ __device__ __forceinline__ void sg_load_rows(bf16* dst, const bf16* src, size_t 
 
 // grid (H * n_seqs, row tiles, C * parts); block BM * 2 threads (a warp per 16 query rows).  C = K with `all_values`, else 1.
 // part[((p * T + t) * H + h) * C + c][vdim] receives the sum over the keys of part p of w_h(t, j) v_c(j).
-template <int HD, int BM>
+// GROUP (a decode step: every sequence brings one token): grid (K * n_seqs, 1, C * parts), and a block's rows are the H / K heads
+// of one kv head instead of tokens, so a key tile is read once for all the heads that share it.
+template <int HD, int BM, bool GROUP>
 __global__ void __launch_bounds__(BM * 2)
 sigmoid_attn_mma_kernel(const bf16* __restrict__ q, long long q_row_stride, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
@@ -191,20 +194,22 @@ sigmoid_attn_mma_kernel(const bf16* __restrict__ q, long long q_row_stride, cons
   bf16* ring = reinterpret_cast<bf16*>(sg_smem);  // SG_NBUF x [SG_BN][STRIDE]
   bf16* q_s = ring + SG_NBUF * SG_BN * STRIDE;     // [BM][STRIDE]
 
-  const int s = blockIdx.x / H, h = blockIdx.x % H;
+  const int rep = H / K;
+  const int s = GROUP ? blockIdx.x / K : blockIdx.x / H;
+  const int h = GROUP ? (blockIdx.x % K) * rep : blockIdx.x % H;  // (GROUP: the first head of the block's rows)
   const int tok0 = seq_start[s];
   const int q_len = seq_start[s + 1] - tok0;
-  const int row0 = (int)(gridDim.y - 1 - blockIdx.y) * BM;  // the row tiles with the most keys start first
+  const int row0 = GROUP ? 0 : (int)(gridDim.y - 1 - blockIdx.y) * BM;  // the row tiles with the most keys start first
   if (row0 >= q_len) return;
   const int C = all_values ? K : 1;
   const int c = blockIdx.z % C, p = blockIdx.z / C;
   const int pos0 = seq_pos0[s];
-  const int kh = h / (H / K);
+  const int kh = h / rep;
   const int vh = all_values ? c : kh;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
-  const int rows_here = min(BM, q_len - row0);
-  const int last_pos = pos0 + row0 + rows_here - 1;
+  const int rows_here = GROUP ? min(BM, rep) : min(BM, q_len - row0);
+  const int last_pos = GROUP ? pos0 : pos0 + row0 + rows_here - 1;
   const int first_pos = pos0 + row0;
   const int lowest_key = rl_first_key(first_pos, window, chunk);
   // the tiles of this block's part of the key range (a part is a run of whole tiles)
@@ -227,7 +232,8 @@ sigmoid_attn_mma_kernel(const bf16* __restrict__ q, long long q_row_stride, cons
       for (int i = tid; i < n16; i += NTHREADS) zp[i] = z;
     }
     __syncthreads();
-    sg_load_rows<NTHREADS>(q_s, q + (size_t)(tok0 + row0) * q_row_stride + (size_t)h * kdim, (size_t)q_row_stride, rows_here, kdim, STRIDE);
+    sg_load_rows<NTHREADS>(q_s, q + (size_t)(tok0 + row0) * q_row_stride + (size_t)h * kdim, GROUP ? (size_t)kdim : (size_t)q_row_stride, rows_here,
+                           kdim, STRIDE);
     const int* table = block_table + (size_t)s * table_width;
     const int n_loads = (tile_hi - tile_lo + 1) * 2;
     auto issue = [&](int n) {
@@ -244,8 +250,12 @@ sigmoid_attn_mma_kernel(const bf16* __restrict__ q, long long q_row_stride, cons
     issue(1);
     sg_cp_async_commit();
 
-    const float bias = head_bias ? head_bias[h] : 0.f;
-    const int qpos[2] = {first_pos + warp * 16 + g, first_pos + warp * 16 + g + 8};
+    float bias[2] = {0.f, 0.f};
+    if (head_bias) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) bias[r] = GROUP ? head_bias[h + min(warp * 16 + g + 8 * r, rows_here - 1)] : head_bias[h];
+    }
+    const int qpos[2] = {GROUP ? pos0 : first_pos + warp * 16 + g, GROUP ? pos0 : first_pos + warp * 16 + g + 8};
     const int qlow[2] = {rl_first_key(qpos[0], window, chunk), rl_first_key(qpos[1], window, chunk)};
     const float inv_cap = softcap > 0.f ? scale / softcap : 0.f;
     float s_acc[SG_BN / 8][4];
@@ -284,7 +294,7 @@ sigmoid_attn_mma_kernel(const bf16* __restrict__ q, long long q_row_stride, cons
             float v = softcap > 0.f ? softcap * rl_tanh_sfu(s_acc[nn][e] * inv_cap) : s_acc[nn][e] * scale;
             const int key = key0 + nn * 8 + 2 * t4 + (e & 1);
             const bool seen = key <= qpos[r] && key >= qlow[r];
-            s_acc[nn][e] = seen ? __fdividef(1.0f, 1.0f + __expf(-(v + bias))) : 0.f;
+            s_acc[nn][e] = seen ? __fdividef(1.0f, 1.0f + __expf(-(v + bias[r]))) : 0.f;
           }
         }
         // ---- O += W V
@@ -312,8 +322,8 @@ sigmoid_attn_mma_kernel(const bf16* __restrict__ q, long long q_row_stride, cons
   for (int r = 0; r < 2; ++r) {
     const int row = warp * 16 + g + 8 * r;
     if (row < rows_here) {
-      const size_t t = (size_t)(tok0 + row0 + row);
-      float* o = part + ((((size_t)p * n_tokens + t) * H + h) * C + c) * vdim;
+      const size_t t = GROUP ? (size_t)tok0 : (size_t)(tok0 + row0 + row);
+      float* o = part + ((((size_t)p * n_tokens + t) * H + (GROUP ? h + row : h)) * C + c) * vdim;
 #pragma unroll
       for (int nn = 0; nn < HD / 8; ++nn) {
         const int d = nn * 8 + 2 * t4;
@@ -359,18 +369,18 @@ __global__ void sigmoid_attn_mix_kernel(const float* __restrict__ part, int part
   }
 }
 
-template <int HD, int BM>
+template <int HD, int BM, bool GROUP>
 static int sg_launch(const bf16* q, long long q_row_stride, const bf16* k_pages, const bf16* v_pages, const int* block_table, int table_width,
                      const int* seq_start, const int* seq_pos0, const float* head_bias, float* part, int n_tokens, int n_seqs, int max_q_len,
                      int H, int K, int kdim, int vdim, int window, float scale, int chunk, float softcap, int all_values, int parts,
                      cudaStream_t stream) {
   const size_t smem = (size_t)(SG_NBUF * SG_BN + BM) * (HD + 8) * sizeof(bf16);
-  auto kern = sigmoid_attn_mma_kernel<HD, BM>;
+  auto kern = sigmoid_attn_mma_kernel<HD, BM, GROUP>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) RL_REFUSE(9, "sigmoid_attn_mma: cannot get %zu bytes of shared memory", smem);
   }
-  dim3 grid(H * n_seqs, (max_q_len + BM - 1) / BM, (all_values ? K : 1) * parts);
+  dim3 grid((GROUP ? K : H) * n_seqs, GROUP ? 1 : (max_q_len + BM - 1) / BM, (all_values ? K : 1) * parts);
   kern<<<grid, BM * 2, smem, stream>>>(q, q_row_stride, k_pages, v_pages, block_table, table_width, seq_start, seq_pos0, head_bias, part,
                                        n_tokens, H, K, kdim, vdim, window, scale, chunk, softcap, all_values, parts);
   RL_LAUNCH_RESULT();
@@ -393,15 +403,22 @@ RL_API int rl_sigmoid_attn_mma(const void* q, long long q_row_stride, const void
   if (mix_smem > 48 * 1024) RL_REFUSE(5, "sigmoid_attn_mma: %d heads of %d values do not fit the second kernel's shared memory", H, vdim);
   const int hd = kdim > vdim ? kdim : vdim;
   const int all_values = mix != nullptr ? 1 : 0;
-  const bool single = max_q_len <= 16;
+  // every sequence brings one token (and a kv head's heads fit a block's rows): the rows of a block are heads
+  const bool group = max_q_len == 1 && n_tokens == n_seqs && H / K <= 64;
+  const bool narrow = group && H / K <= 16;
   int rc;
-#define SG_GO(HD, BM)                                                                                                                      \
-  rc = sg_launch<HD, BM>((const bf16*)q, q_row_stride, (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_width, seq_start,   \
-                         seq_pos0, head_bias, part, n_tokens, n_seqs, max_q_len, H, K, kdim, vdim, window, scale, chunk, softcap,          \
-                         all_values, parts, stream)
-  if (hd <= 32) { if (single) SG_GO(32, 16); else SG_GO(32, 64); }
-  else if (hd <= 64) { if (single) SG_GO(64, 16); else SG_GO(64, 64); }
-  else { if (single) SG_GO(128, 16); else SG_GO(128, 64); }
+#define SG_GO(HD, BM, GROUP)                                                                                                               \
+  rc = sg_launch<HD, BM, GROUP>((const bf16*)q, q_row_stride, (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_width,       \
+                                seq_start, seq_pos0, head_bias, part, n_tokens, n_seqs, max_q_len, H, K, kdim, vdim, window, scale, chunk, \
+                                softcap, all_values, parts, stream)
+#define SG_PICK(HD)                          \
+  if (narrow) SG_GO(HD, 16, true);           \
+  else if (group) SG_GO(HD, 64, true);       \
+  else SG_GO(HD, 64, false)
+  if (hd <= 32) { SG_PICK(32); }
+  else if (hd <= 64) { SG_PICK(64); }
+  else { SG_PICK(128); }
+#undef SG_PICK
 #undef SG_GO
   if (rc != 0) return rc;
   int threads = H * vdim;

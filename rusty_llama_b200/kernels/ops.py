@@ -1810,17 +1810,18 @@ def short_conv(
     x: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], slot_ids: torch.Tensor, seq_start: torch.Tensor, tok_seq: torch.Tensor,
     silu: bool = True,
 ) -> torch.Tensor:
-    """y[t, c] = act(sum_i w[c, i] x[t - taps + 1 + i, c]) over each sequence's tokens, a causal convolution over time per channel.
+    """y[t, c] = act(sum_i w[i, c] x[t - taps + 1 + i, c]) over each sequence's tokens, a causal convolution over time per channel.
 
-    x: [T, C] rows (a view of a projection's rows is taken as it is).  w: float32 [C, taps], the last column the current token's.
+    x: [T, C] rows (a view of a projection's rows is taken as it is).  w: float32 [taps, C] (tap i of every channel side by side,
+    so that neighbouring channels read neighbouring weights), the last row the current token's.
     state: float32 [slots, taps - 1, C], the last taps - 1 inputs of every sequence before this step (zeros at a sequence's
     start); it is moved on to the end of the step's tokens.  Returns [T, C] in x's type."""
     _cuda(x, "short_conv x", contiguous=False)
     xs = _rows(x, "short_conv x")
     T, C = x.shape
     _cuda(w, "short_conv w", torch.float32)
-    _need(w.dim() == 2 and w.shape[0] == C, f"short_conv: w {tuple(w.shape)} does not have {C} rows")
-    taps = w.shape[1]
+    _need(w.dim() == 2 and w.shape[1] == C, f"short_conv: w {tuple(w.shape)} does not have {C} columns")
+    taps = w.shape[0]
     _need(1 <= taps <= SHORT_CONV_MAX_TAPS, f"short_conv: {taps} taps (1 to {SHORT_CONV_MAX_TAPS})")
     _cuda(slot_ids, "short_conv slot_ids", torch.int32)
     _cuda(seq_start, "short_conv seq_start", torch.int32)

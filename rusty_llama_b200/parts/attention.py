@@ -322,7 +322,7 @@ class Attention(Mixer):
                 keys = min(self.window, step.plan_kv_len) if self.window else step.plan_kv_len
                 keys = min(self.chunk, keys) if self.chunk else keys
                 pages = (keys + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE + (1 if (self.window or self.chunk) else 0)
-                blocks = step.n_seqs * self.H * (self.K if mixed else 1)
+                blocks = step.n_seqs * self.K * (self.K if mixed else 1)  # a block's rows are the heads of one kv head
                 parts = max(1, min(4 * sm_count(proj.device) // max(blocks, 1), pages, 64))
             scratch = self.rt.workspace.get("sigmoid_attn_parts", ops.sigmoid_attn_mma_scratch_floats(T, self.H, self.K, self.vd, mixed, parts), torch.float32)
             return ops.sigmoid_attn_mma(

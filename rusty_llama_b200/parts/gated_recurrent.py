@@ -291,7 +291,8 @@ class GatedDeltaRule(Mixer):
         p, n = self.prefix, self.names
         # one product serves q, k, v, the output gate and the two scalars of every head
         self.w_in = torch.cat([tensors[p + n[key]] for key in ("q", "k", "v", "gate", "b", "a")], dim=0).contiguous()
-        self.w_conv = torch.cat([tensors[p + n[key] + n["conv"]] for key in ("q", "k", "v")], dim=0).contiguous()
+        # (stored [channels, taps]; the kernel reads [taps, channels], neighbouring channels side by side)
+        self.w_conv = torch.cat([tensors[p + n[key] + n["conv"]] for key in ("q", "k", "v")], dim=0).t().contiguous()
         self.a_log, self.dt_bias = tensors[p + n["a_log"]].contiguous(), tensors[p + n["dt_bias"]].contiguous()
         self.w_norm = tensors[p + n["norm"]].contiguous()
         self.w_o = tensors[p + n["o"]].contiguous()

@@ -210,7 +210,7 @@ def test_short_convolution_through_its_record(dtype, taps):
         parts = [xs[i][at[i] : at[i] + portion[i]] for i in range(2)]
         x = torch.zeros((sum(portion), C + 5), dtype=dtype, device="cuda")
         x[:, :C] = _dev(np.concatenate(parts), dtype)
-        y = ops.short_conv(x[:, :C], _dev(w, torch.float32), state, slots, _i32([0, portion[0], sum(portion)]), _i32([0] * portion[0] + [1] * portion[1]))
+        y = ops.short_conv(x[:, :C], _dev(w, torch.float32).t().contiguous(), state, slots, _i32([0, portion[0], sum(portion)]), _i32([0] * portion[0] + [1] * portion[1]))
         got[0].append(y[: portion[0]].to(F64).cpu().numpy())
         got[1].append(y[portion[0] :].to(F64).cpu().numpy())
         at = [at[i] + portion[i] for i in range(2)]
