@@ -38,7 +38,7 @@ TAPS = 4
 def namalix_config(z: dict) -> dict:
     H, G, hd = z["heads"], z["kv_heads"], z["hd"]
     attn = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": 1.0 / math.sqrt(hd), "softcap": 30.0, "v_mix": True,
-            "rot": {"base": 10000.0, "dims": hd // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+            "rot": {"base": 10000.0, "dims": hd // 2, "scaling": {"factor": 8.0, "original": 8192, "fast": 16.0, "slow": 2.0}}}
     ret = {"heads": H, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** (-3 - 5 * i / max(H - 1, 1)) for i in range(H)], "rot": {"base": 1000000.0, "dims": hd}}
     delta = {"heads": H, "kv_heads": H, "dim": hd, "vdim": hd, "conv": TAPS}
     dense = {"kind": "dense", "ff": z["top"] * z["eff"]}

@@ -76,7 +76,7 @@ def config_c():
         "architecture": "Namalix", "vocab": 160, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 8.0},
         "layers": [
             {"type": "attention", "mixer": _attn(4, 2, 64, 64, _rot(10000.0, 32, yarn), 0.125, 20.0, True), "mlp": _dense(256)},
-            {"type": "retention", "mixer": _ret(2, 64, 64, [0.95, 0.995], _rot(1000000.0, 64)), "mlp": _moe(8, 2, 1.5, 64, 1.5)},
+            {"type": "retention", "mixer": _ret(2, 64, 64, [0.95, 0.995], _rot(1000000.0, 64)), "mlp": _moe(8, 3, 1.25, 48, 2.0)},
             {"type": "delta", "mixer": _delta(2, 1, 128, 64, 4), "mlp": _moe(4, 1, 2.0, 128, 3.0)},
             {"type": "attention", "mixer": _attn(8, 2, 32, 64, _rot(10000.0, 32, yarn), 0.18, 10.0, True), "mlp": _dense(128)},
         ],
