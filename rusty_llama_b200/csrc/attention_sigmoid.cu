@@ -335,37 +335,35 @@ sigmoid_attn_mma_kernel(const bf16* __restrict__ q, long long q_row_stride, cons
 
 // out[t][h][:] = out_scale * logistic(gate[t][h]) * sum_p sum_g mix[h][g] part[p][t][g][kv(h)][:]   (with a mixing matrix)
 //              = out_scale * logistic(gate[t][h]) * sum_p part[p][t][h][0][:]                         (without)
-// One block per token; the sums over the parts of one kv head at a time in shared memory, then a thread per (head, value).
+// A block per (token, kv head c): the sums over the parts of all heads' P[.][c] in shared memory (every load in flight at once),
+// then a thread per (head of kv head c, value).  Without a mixing matrix C = 1 and the block makes all heads.
 __global__ void sigmoid_attn_mix_kernel(const float* __restrict__ part, int parts, const float* __restrict__ mix, const bf16* __restrict__ gate,
                                         int gate_stride, float out_scale, bf16* __restrict__ out, int out_stride, int n_tokens, int H, int K,
                                         int vdim) {
   extern __shared__ float sums[];  // [H][vdim]
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, c = blockIdx.y;
   const int rep = H / K, C = mix ? K : 1;
-  for (int c = 0; c < C; ++c) {
-    __syncthreads();
-    for (int i = threadIdx.x; i < H * vdim; i += blockDim.x) {
-      const int gh = i / vdim, d = i - gh * vdim;
-      float acc = 0.f;
-      for (int p = 0; p < parts; ++p) acc += part[((((size_t)p * n_tokens + t) * H + gh) * C + c) * vdim + d];
-      sums[i] = acc;
+  for (int i = threadIdx.x; i < H * vdim; i += blockDim.x) {
+    const int gh = i / vdim, d = i - gh * vdim;
+    float acc = 0.f;
+    for (int p = 0; p < parts; ++p) acc += part[((((size_t)p * n_tokens + t) * H + gh) * C + c) * vdim + d];
+    sums[i] = acc;
+  }
+  __syncthreads();
+  const int n_heads = mix ? rep : H;  // the heads whose values are kv head c's (all heads when nothing is mixed)
+  for (int i = threadIdx.x; i < n_heads * vdim; i += blockDim.x) {
+    const int hl = i / vdim, d = i - hl * vdim;
+    const int h = mix ? c * rep + hl : hl;
+    float acc;
+    if (mix) {
+      acc = 0.f;
+      for (int gh = 0; gh < H; ++gh) acc += mix[h * H + gh] * sums[gh * vdim + d];
+    } else {
+      acc = sums[h * vdim + d];
     }
-    __syncthreads();
-    const int n_heads = mix ? rep : H;  // the heads whose values are kv head c's (all heads when nothing is mixed)
-    for (int i = threadIdx.x; i < n_heads * vdim; i += blockDim.x) {
-      const int hl = i / vdim, d = i - hl * vdim;
-      const int h = mix ? c * rep + hl : hl;
-      float acc;
-      if (mix) {
-        acc = 0.f;
-        for (int gh = 0; gh < H; ++gh) acc += mix[h * H + gh] * sums[gh * vdim + d];
-      } else {
-        acc = sums[h * vdim + d];
-      }
-      float gv = out_scale;
-      if (gate) gv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + h])));
-      out[(size_t)t * out_stride + (size_t)h * vdim + d] = __float2bfloat16_rn(acc * gv);
-    }
+    float gv = out_scale;
+    if (gate) gv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + h])));
+    out[(size_t)t * out_stride + (size_t)h * vdim + d] = __float2bfloat16_rn(acc * gv);
   }
 }
 
@@ -423,7 +421,8 @@ RL_API int rl_sigmoid_attn_mma(const void* q, long long q_row_stride, const void
   if (rc != 0) return rc;
   int threads = H * vdim;
   threads = threads > 512 ? 512 : ((threads + 31) / 32) * 32;
-  sigmoid_attn_mix_kernel<<<n_tokens, threads, mix_smem, stream>>>(part, parts, mix, (const bf16*)gate, gate_stride, out_scale, (bf16*)out,
-                                                                   out_stride, n_tokens, H, K, vdim);
+  if (n_tokens > 2147483647 / 1 || (mix ? K : 1) > 65535) RL_REFUSE(10, "sigmoid_attn_mma: the second kernel's grid is too large");
+  sigmoid_attn_mix_kernel<<<dim3(n_tokens, mix ? K : 1), threads, mix_smem, stream>>>(part, parts, mix, (const bf16*)gate, gate_stride, out_scale,
+                                                                                      (bf16*)out, out_stride, n_tokens, H, K, vdim);
   RL_LAUNCH_RESULT();
 }
