@@ -83,7 +83,27 @@ def config_c():
     }
 
 
-CONFIGS = {"a": config_a, "b": config_b, "c": config_c}
+def config_d():
+    """Seven layers of larger and odd sizes in another order: a delta layer first (6 heads on 3 q/k heads, keys of 48: a last row slice
+    that is half empty, five taps), an attention layer outside the value mixing BEFORE its source, 10 heads on 5 and 16 on 4,
+    keys of 48 and values of 24 and 40 (padded tiles of the tensor-core kernel), five retention heads with rotated halves of
+    24, a state of 128 x 96, twelve experts of which three, all of four, one of three."""
+    yarn = {"factor": 16.0, "original": 512, "fast": 24.0, "slow": 0.5}
+    return {
+        "architecture": "Namalix", "vocab": 1000, "width": 320, "norm": {"eps": 1e-5}, "embedding": {"scale": 11.0},
+        "layers": [
+            {"type": "delta", "mixer": _delta(6, 3, 48, 40, 5), "mlp": _moe(6, 2, 2.0, 96, 2.0)},
+            {"type": "attention", "mixer": _attn(10, 5, 48, 24, _rot(50000.0, 24, yarn), 0.2, 15.0, False), "mlp": _dense(512)},
+            {"type": "attention", "mixer": _attn(12, 4, 32, 40, _rot(10000.0, 32, yarn), 0.22, 50.0, True), "mlp": _moe(4, 4, 1.0, 128, 0.9)},
+            {"type": "retention", "mixer": _ret(5, 48, 24, [0.8, 0.9, 0.99, 0.999, 0.9999], _rot(10000.0, 24)), "mlp": None},
+            {"type": "attention", "mixer": _attn(4, 4, 64, 40, _rot(10000.0, 16), 0.125, 8.0, True), "mlp": _dense(200)},
+            {"type": "delta", "mixer": _delta(2, 2, 128, 96, 2), "mlp": _moe(12, 3, 0.5, 64, 4.0)},
+            {"type": "attention", "mixer": _attn(16, 4, 32, 40, _rot(1000.0, 8), 0.3, 30.0, True), "mlp": _moe(3, 1, 3.0, 256, 1.0)},
+        ],
+    }
+
+
+CONFIGS = {"a": config_a, "b": config_b, "c": config_c, "d": config_d}
 
 
 def tensor_shapes(cfg):
